@@ -1,0 +1,129 @@
+/*
+ * sage_b200.h - C ABI of the B200 (sm_100a) SageAttention forward path.
+ *
+ * Every entry point takes plain device pointers, sizes, element strides and a
+ * CUDA stream (passed as void*, i.e. a cudaStream_t); nothing here depends on
+ * torch.  All functions return SAGE_B200_OK (0) or a negative error code and leave a
+ * human-readable message retrievable with sage_b200_last_error() (thread-local).
+ * Nothing is allocated or freed on the caller's behalf; kernels are enqueued on the
+ * given stream and the call returns without synchronising.
+ *
+ * Tensor convention: a "4-D tensor" is addressed as
+ *     base + b*stride[0] + h*stride[1] + n*stride[2] + d          (d contiguous)
+ * with strides in ELEMENTS, which covers both layouts of the reference
+ * ("NHD" = (B,N,H,D) and "HND" = (B,H,N,D), sageattention/cuda_attn.py:156-165).
+ *
+ * Each declaration cites the interface of the reference
+ * (woct0rdho/sageattention-autotune) that it replaces.
+ */
+#ifndef SAGE_B200_H_
+#define SAGE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAGE_B200_VERSION 100
+
+/* error codes */
+#define SAGE_B200_OK               0
+#define SAGE_B200_ERR_INVALID     -1   /* bad argument (shape, dtype, stride, alignment) */
+#define SAGE_B200_ERR_UNSUPPORTED -2   /* valid in the reference, not built here yet */
+#define SAGE_B200_ERR_CUDA        -3   /* a CUDA runtime/driver call failed */
+#define SAGE_B200_ERR_DEVICE      -4   /* the kernel reported a device-side failure (bounded wait ran out) */
+
+/* element types of the 16-bit tensors */
+#define SAGE_B200_F16  0
+#define SAGE_B200_BF16 1
+
+/* which rows share one int8 scale (sage_b200_quant_int8: group_kind) */
+#define SAGE_B200_GROUP_Q_THREAD 0  /* reference Q grouping: rows r with equal r%8 inside a WARPQ-row block */
+#define SAGE_B200_GROUP_K_THREAD 1  /* reference K grouping: row pairs, (r%8)/2, inside a WARPK-row block */
+#define SAGE_B200_GROUP_BLOCK    2  /* one scale per BLK x D tile */
+
+/* how x/scale is evaluated */
+#define SAGE_B200_DIV_FULL 0   /* div.full.f32, what the reference's Triton kernels compile to on a GPU */
+#define SAGE_B200_DIV_IEEE 1   /* correctly rounded, what a CPU evaluation of the same source gives */
+
+/* scale granularity the attention kernel assumes (must match how Q/K were quantised) */
+#define SAGE_B200_GRAN_PER_THREAD 0
+#define SAGE_B200_GRAN_PER_BLOCK  1
+
+/* accumulation mode of P.V (pv_accum_dtype of the reference API) */
+#define SAGE_B200_PV_F32     0   /* "fp32"      */
+#define SAGE_B200_PV_F16     1   /* "fp16"      */
+#define SAGE_B200_PV_F16_F32 2   /* "fp16+fp32" */
+
+int sage_b200_version(void);
+const char* sage_b200_last_error(void);
+
+/*
+ * Channel mean of K over the sequence, rounded to K's dtype.
+ * Replaces `km = k.mean(dim=seq_dim, keepdim=True)` (sageattention/cuda_attn.py:167-170).
+ *   k        16-bit (batch, heads, len, head_dim) by strides
+ *   km       out, (batch, heads, head_dim) contiguous, same dtype as k
+ *   scratch  device buffer of at least sage_b200_mean_k_scratch_bytes(...) bytes holding
+ *            the per-slice fp32 partial sums of the two-stage reduction
+ */
+size_t sage_b200_mean_k_scratch_bytes(int batch, int heads, int len, int head_dim);
+int sage_b200_mean_k(const void* k, void* km, void* scratch, size_t scratch_bytes, int dtype,
+                     int batch, int heads, int len, int head_dim, const int64_t k_strides[3],
+                     void* stream);
+
+/*
+ * int8 quantisation of Q or K with fp32 scales.
+ * Replaces quant_query_per_thread_int8_kernel / quant_key_per_thread_int8_kernel
+ * (sageattention/triton/quant_per_thread.py:22-115, host wrapper :118-205) and
+ * quant_per_block_int8_kernel (sageattention/triton/quant_per_block.py:32-78, :81-173).
+ *   x        16-bit input by strides;  mean: (batch, heads, head_dim) contiguous or NULL
+ *   out      int8, same logical shape, by out_strides
+ *   scale    fp32 (batch, heads, groups) contiguous with
+ *            groups = ceil(len/blk) * (blk/warp) * {8 | 4}   for the two per-thread kinds,
+ *            groups = ceil(len/blk)                           for SAGE_B200_GROUP_BLOCK
+ *   blk      BLKQ or BLKK of the attention tile config (32, 64 or 128)
+ *   warp     WARPQ or WARPK (8..blk, a power of two); ignored for SAGE_B200_GROUP_BLOCK
+ * Rows past `len` inside the last block behave like the reference's masked loads:
+ * they read as 0, the mean is still subtracted from them, they enter the maximum and
+ * are not stored.
+ */
+int sage_b200_quant_int8(const void* x, const void* mean, int8_t* out, float* scale, int dtype,
+                         int batch, int heads, int len, int head_dim,
+                         const int64_t x_strides[3], const int64_t out_strides[3],
+                         int blk, int warp, int group_kind, int div_mode, void* stream);
+
+/*
+ * V cast to fp16.  Replaces `v.to(torch.float16)` (sageattention/cuda_attn.py:195,233,250).
+ */
+int sage_b200_cast_v_f16(const void* v, void* out, int dtype, int batch, int heads, int len,
+                         int head_dim, const int64_t v_strides[3], const int64_t out_strides[3],
+                         void* stream);
+
+/*
+ * Attention core on quantised Q/K and fp16 V.
+ * Replaces torch.ops.sageattention_qattn_sm80.qk_int8_sv_f16_accum_f32_attn,
+ * ..._accum_f16_attn and ..._accum_f16_attn_inst_buf (csrc/qattn/pybind_sm80.cpp:24-98,
+ * csrc/qattn/qk_int8_sv_f16_launch_sm80.cuh:244-308), selected by `pv_accum`.
+ *   q, k       int8 by strides;  v: fp16 by strides;  out: out_dtype by strides
+ *   q_scale    fp32 (batch, heads_q, q_groups), k_scale fp32 (batch, heads_kv, k_groups), laid
+ *              out as sage_b200_quant_int8 writes them for (blk_q, warp_q) / (blk_k, warp_k)
+ *   lse        NULL, or fp32 (batch, heads_q, len_q): log2(sum) + max in base 2, as the
+ *              reference kernel defines it (qk_int8_sv_f16_kernel_sm80.cuh:645-656)
+ *   status     NULL, or 4 int32 on the device, zeroed by the caller; the kernel writes a
+ *              non-zero code there if one of its bounded waits ran out
+ *   causal     top-left aligned: key j is visible to query i iff j <= i
+ */
+int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* out,
+                       const float* q_scale, const float* k_scale, float* lse, int32_t* status,
+                       int out_dtype, int batch, int heads_q, int heads_kv, int len_q, int len_kv,
+                       int head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
+                       const int64_t v_strides[3], const int64_t o_strides[3], int is_causal,
+                       float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k,
+                       int granularity, int pv_accum, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGE_B200_H_ */

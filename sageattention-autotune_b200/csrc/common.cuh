@@ -1,0 +1,54 @@
+// Shared host/device helpers of the B200 SageAttention kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/sage_b200.h"
+
+namespace sage {
+
+// Thread-local message behind sage_b200_last_error().
+char* error_buffer();
+int fail(int code, const char* fmt, ...);
+
+#define SAGE_CUDA_TRY(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess)                                                               \
+      return ::sage::fail(SAGE_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+#define SAGE_REQUIRE(cond, ...)                                           \
+  do {                                                                    \
+    if (!(cond)) return ::sage::fail(SAGE_B200_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// 16-bit storage -> fp32 (exact for both types).
+template <int DTYPE>
+__device__ __forceinline__ float to_f32(unsigned short bits) {
+  if constexpr (DTYPE == SAGE_B200_BF16) {
+    return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+  } else {
+    return __half2float(__ushort_as_half(bits));
+  }
+}
+
+template <int DTYPE>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&x)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i + 0] = to_f32<DTYPE>(static_cast<unsigned short>(w[i] & 0xffffu));
+    x[2 * i + 1] = to_f32<DTYPE>(static_cast<unsigned short>(w[i] >> 16));
+  }
+}
+
+}  // namespace sage

@@ -1,0 +1,92 @@
+"""ctypes binding of libsage_b200.so (declared in include/sage_b200.h).
+
+This is the only place the Python package touches native code.  There is no fallback: if the
+library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libsage_b200.so")
+
+F16, BF16 = 0, 1
+GROUP_Q_THREAD, GROUP_K_THREAD, GROUP_BLOCK = 0, 1, 2
+DIV_FULL, DIV_IEEE = 0, 1
+GRAN_PER_THREAD, GRAN_PER_BLOCK = 0, 1
+PV_F32, PV_F16, PV_F16_F32 = 0, 1, 2
+
+EXPORTS = (
+    "sage_b200_version", "sage_b200_last_error", "sage_b200_mean_k_scratch_bytes", "sage_b200_mean_k",
+    "sage_b200_quant_int8", "sage_b200_cast_v_f16", "sage_b200_attn_fwd",
+)
+
+_lib = None
+_I64x3 = ctypes.c_int64 * 3
+
+
+class SageB200Error(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise ImportError(
+                f"{_LIB_PATH} is missing: build it with `python sageattention-autotune_b200/build.py` "
+                "(there is no non-CUDA fallback)")
+        L = ctypes.CDLL(_LIB_PATH)
+        vp, i, i64p, f = ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int64), ctypes.c_float
+        L.sage_b200_version.restype = i
+        L.sage_b200_last_error.restype = ctypes.c_char_p
+        L.sage_b200_mean_k_scratch_bytes.restype = ctypes.c_size_t
+        L.sage_b200_mean_k_scratch_bytes.argtypes = [i, i, i, i]
+        L.sage_b200_mean_k.restype = i
+        L.sage_b200_mean_k.argtypes = [vp, vp, vp, ctypes.c_size_t, i, i, i, i, i, i64p, vp]
+        L.sage_b200_quant_int8.restype = i
+        L.sage_b200_quant_int8.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i64p, i64p, i, i, i, i, vp]
+        L.sage_b200_cast_v_f16.restype = i
+        L.sage_b200_cast_v_f16.argtypes = [vp, vp, i, i, i, i, i, i64p, i64p, vp]
+        L.sage_b200_attn_fwd.restype = i
+        L.sage_b200_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i,
+                                         i64p, i64p, i64p, i64p, i, f, i, i, i, i, i, i, vp]
+        _lib = L
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise SageB200Error(f"sage_b200 error {rc}: {lib().sage_b200_last_error().decode()}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float16:
+        return F16
+    if dt == torch.bfloat16:
+        return BF16
+    raise ValueError(f"Unsupported dtype: {dt}")
+
+
+def bhn_strides(t: torch.Tensor, tensor_layout: str):
+    """Element strides in (batch, head, seq) order for either layout."""
+    if tensor_layout == "HND":
+        return _I64x3(t.stride(0), t.stride(1), t.stride(2))
+    return _I64x3(t.stride(0), t.stride(2), t.stride(1))
+
+
+def bhnd(t: torch.Tensor, tensor_layout: str):
+    if tensor_layout == "HND":
+        b, h, n, d = t.shape
+    elif tensor_layout == "NHD":
+        b, n, h, d = t.shape
+    else:
+        raise ValueError("tensor_layout must be 'NHD' or 'HND'.")
+    return b, h, n, d
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,180 @@
+"""Public API: drop-in for `sageattention` of woct0rdho/sageattention-autotune.
+
+Mirrors sageattention/core.py:6-21 (names and placeholders) and sageattention/cuda_attn.py:44-274
+(argument checks, head-dim padding, K smoothing, quantisation, accumulate-mode dispatch, LSE
+fix-up) on top of the sm_100a kernels.  Differences from the reference, all additive:
+`sm_scale` keyword (default head_dim**-0.5), `qk_quant_gran` keyword ("per_thread" is what the
+reference's CUDA backend uses, "per_block" what its Triton backend uses), a working `return_lse`.
+"""
+from __future__ import annotations
+
+import os
+import warnings
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _capi as C
+from .quant import cast_v_fp16, mean_k, per_block_int8, per_thread_int8
+from .tile_table import SUPPORTED_QK_CONFIGS, select_qk_config
+
+LOG2_E = 1.44269504088896340736
+
+DEFAULT_PV_ACCUM_DTYPE = os.getenv("SAGEATTN_DEFAULT_PV_ACCUM_DTYPE", "fp32").lower()
+if DEFAULT_PV_ACCUM_DTYPE not in ("fp32", "fp16", "fp16+fp32"):
+    DEFAULT_PV_ACCUM_DTYPE = "fp32"
+
+_PV_CODE = {"fp32": C.PV_F32, "fp16": C.PV_F16, "fp16+fp32": C.PV_F16_F32}
+
+
+def _check_status_enabled() -> bool:
+    return os.getenv("SAGE_B200_CHECK", "0").lower() in ("1", "true", "yes", "on")
+
+
+def _padded_head_dim(head_dim: int) -> int:
+    for edge in (64, 128, 256):
+        if head_dim <= edge:
+            return edge
+    raise ValueError(f"Unsupported head_dim: {head_dim}")
+
+
+def _pad_qkv(q, k, v):
+    head_dim = q.size(-1)
+    pad_to = _padded_head_dim(head_dim)
+    if pad_to == head_dim:
+        return head_dim, q, k, v
+    pad = (0, pad_to - head_dim)
+    return head_dim, F.pad(q, pad), F.pad(k, pad), F.pad(v, pad)
+
+
+def _lse_correction(q, km, tensor_layout):
+    """q . km^T per query row, fp32, with GQA broadcast (reference: utils.py:39-49)."""
+    h_dim = 1 if tensor_layout == "HND" else 2
+    rep = q.size(h_dim) // km.size(h_dim)
+    if rep > 1:
+        km = torch.repeat_interleave(km, rep, dim=h_dim)
+    if tensor_layout == "NHD":
+        corr = torch.matmul(q.transpose(1, 2), km.permute(0, 2, 3, 1)).squeeze(-1)
+    else:
+        corr = torch.matmul(q, km.transpose(2, 3)).squeeze(-1)
+    return corr.to(torch.float32)
+
+
+def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_layout, is_causal, sm_scale,
+                       qk_config, pv_accum_dtype="fp32", return_lse=False, granularity="per_thread"):
+    """The attention core on pre-quantised tensors; the counterpart of
+    torch.ops.sageattention_qattn_sm80.qk_int8_sv_f16_accum_*_attn (csrc/qattn/pybind_sm80.cpp:24-98).
+    Writes `output` in place and returns the base-2 LSE ((0,)-shaped when not requested)."""
+    if pv_accum_dtype not in _PV_CODE:
+        raise ValueError("pv_accum_dtype must be 'fp32', 'fp16', or 'fp16+fp32'.")
+    b, hq, nq, d = C.bhnd(q_int8, tensor_layout)
+    _, hkv, nk, _ = C.bhnd(k_int8, tensor_layout)
+    blk_q, blk_k, warp_q, warp_k = qk_config
+    dev = q_int8.device
+    lse = torch.empty((b, hq, nq) if return_lse else (0,), dtype=torch.float32, device=dev)
+    check = _check_status_enabled()
+    status = torch.zeros(4, dtype=torch.int32, device=dev) if check else None
+    with torch.cuda.device(dev):
+        C.check(C.lib().sage_b200_attn_fwd(
+            q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), output.data_ptr(),
+            q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
+            status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
+            C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
+            C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
+            1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k,
+            C.GRAN_PER_THREAD if granularity == "per_thread" else C.GRAN_PER_BLOCK,
+            _PV_CODE[pv_accum_dtype], C.stream_ptr(dev)))
+    if check:
+        st = status.tolist()
+        if st[0] != 0:
+            raise C.SageB200Error(f"attention kernel gave up waiting (code {st[0]}) in CTA {tuple(st[1:])}")
+    return lse
+
+
+def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v, return_lse,
+                         qk_config, sm_scale: Optional[float] = None, qk_quant_gran: str = "per_thread"):
+    """Same contract as the reference's _sageattn_configured (cuda_attn.py:126-274)."""
+    dtype = q.dtype
+    if not q.is_cuda:
+        raise ValueError("Input tensors must be CUDA tensors.")
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError(f"Unsupported dtype: {dtype}")
+    if q.device != k.device or q.device != v.device:
+        raise ValueError("All tensors must be on the same device.")
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise ValueError("All tensors must have the same dtype.")
+    if k.shape != v.shape:
+        raise ValueError("k and v must have the same shape.")
+    if tensor_layout not in ("NHD", "HND"):
+        raise ValueError("tensor_layout must be 'NHD' or 'HND'.")
+    if pv_accum_dtype not in _PV_CODE:
+        raise ValueError("pv_accum_dtype must be 'fp32', 'fp16', or 'fp16+fp32'.")
+    if qk_quant_gran not in ("per_thread", "per_block"):
+        raise ValueError("qk_quant_gran must be 'per_thread' or 'per_block'.")
+
+    head_dim, q, k, v = _pad_qkv(q, k, v)
+    if q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1:
+        raise ValueError("Last dimension of q, k, and v must be contiguous.")
+    if sm_scale is None:
+        sm_scale = head_dim ** -0.5
+
+    if smooth_v:
+        if pv_accum_dtype in ("fp32", "fp16+fp32"):
+            warnings.warn("pv_accum_dtype is fp32 or fp16+fp32, smooth_v will be ignored.", stacklevel=2)
+            smooth_v = False
+        else:
+            raise NotImplementedError("smooth_v with pv_accum_dtype='fp16' is not built for sm_100a yet.")
+
+    # TMA and the vector kernels need 16-byte aligned rows
+    def _aligned(t):
+        return t if (t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
+    q, k, v = _aligned(q), _aligned(k), _aligned(v)
+
+    km = mean_k(k, tensor_layout) if smooth_k else None
+    blk_q, blk_k, warp_q, warp_k = qk_config
+    if qk_quant_gran == "per_thread":
+        q_int8, q_scale, k_int8, k_scale = per_thread_int8(q, k, km, blk_q, warp_q, blk_k, warp_k, tensor_layout)
+    else:
+        q_int8, q_scale, k_int8, k_scale = per_block_int8(q, k, km, blk_q, blk_k, tensor_layout)
+
+    output = torch.empty(q.size(), dtype=dtype, device=q.device)
+    lse = attn_fwd_quantized(q_int8, k_int8, cast_v_fp16(v, tensor_layout), output, q_scale, k_scale,
+                             tensor_layout, is_causal, sm_scale, qk_config, pv_accum_dtype, return_lse,
+                             qk_quant_gran)
+    output = output[..., :head_dim]
+    if not return_lse:
+        return output
+    lse = lse / LOG2_E
+    if smooth_k:
+        lse = lse + _lse_correction(q, km, tensor_layout) * sm_scale
+    return output, lse
+
+
+def sageattn_qk_int8_pv_fp16_cuda(q, k, v, tensor_layout="HND", is_causal=False,
+                                  pv_accum_dtype=DEFAULT_PV_ACCUM_DTYPE, smooth_k=True, smooth_v=False,
+                                  return_lse=False, attn_mask=None, sm_scale: Optional[float] = None,
+                                  qk_quant_gran: str = "per_thread"):
+    """SageAttention forward: int8 Q.K^T, fp16 P.V.  Signature of the reference
+    (cuda_attn.py:44-55) plus the keyword-only extras `sm_scale` and `qk_quant_gran`."""
+    assert attn_mask is None
+    if torch.compiler.is_compiling() and not return_lse:
+        from .ops import sageattn_fixed
+        return sageattn_fixed(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v,
+                              -1.0 if sm_scale is None else float(sm_scale), qk_quant_gran)
+    kv_len = k.size(2) if tensor_layout == "HND" else k.size(1)
+    qk_config = select_qk_config(_padded_head_dim(q.size(-1)), is_causal, pv_accum_dtype, kv_len)
+    return _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v,
+                                return_lse, qk_config, sm_scale, qk_quant_gran)
+
+
+C.lib()  # fail at import time if the native library is missing
+
+sageattn = sageattn_qk_int8_pv_fp16_cuda
+
+# Names other libraries probe for (reference: core.py:18-21).  The Triton backend is not part of
+# this package; fp8 PV and varlen are not built yet.
+sageattn_qk_int8_pv_fp16_triton = None
+sageattn_qk_int8_pv_fp8_cuda = None
+sageattn_qk_int8_pv_fp8_cuda_sm90 = None
+sageattn_varlen = None

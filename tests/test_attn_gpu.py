@@ -1,0 +1,188 @@
+"""GPU parity of the attention core and of the whole sageattn call.
+
+Tolerance (stated by the task): cosine similarity >= 0.9995 and max-abs error <= 2e-2 in the
+output dtype's range, against (a) the CPU oracle fed the same int8 tensors and scales and
+(b) the reference's sm80 CUDA kernel rebuilt for sm_100 (oracle/_ref) on the same inputs.
+"""
+import pytest
+import torch
+
+from gpu_util import cuda_or_fail, make_qkv, reference_ops
+from oracle import sage_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+COS_MIN = 0.9995
+MAX_ABS = 2e-2
+CFG = (128, 64, 32, 64)
+
+
+def _run_core(q, k, v, layout, causal, mode, gran="per_thread", sm_scale=None, return_lse=False, smooth=True):
+    from sageattention import quant
+    from sageattention.core import attn_fwd_quantized
+    km = quant.mean_k(k, layout) if smooth else None
+    if gran == "per_thread":
+        q8, qs, k8, ks = quant.per_thread_int8(q, k, km, *[CFG[i] for i in (0, 2, 1, 3)], layout, div="ieee")
+    else:
+        q8, qs, k8, ks = quant.per_block_int8(q, k, km, 128, 64, layout, div="ieee")
+    v16 = quant.cast_v_fp16(v, layout)
+    out = torch.empty_like(q)
+    sc = sm_scale if sm_scale is not None else q.size(-1) ** -0.5
+    lse = attn_fwd_quantized(q8, k8, v16, out, qs, ks, layout, causal, sc, CFG, mode, return_lse, gran)
+    torch.cuda.synchronize()
+    return out, lse, (q8, qs, k8, ks, v16)
+
+
+def _oracle(quantised, layout, causal, mode, gran, dtype, sm_scale=None):
+    q8, qs, k8, ks, v16 = [t.cpu() for t in quantised]
+    return O.attend(q8, k8, v16, qs, ks, layout, causal, sm_scale, mode, gran, 128, 32, 64, 64, dtype, True)
+
+
+def _assert_close(got, exp, what):
+    c = O.compare(got.cpu(), exp.cpu())
+    assert c["cos"] >= COS_MIN and c["max_abs"] <= MAX_ABS, (what, c)
+    return c
+
+
+@pytest.mark.parametrize("mode", ["fp32", "fp16+fp32", "fp16"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D,dtype,layout", [(128, torch.float16, "HND"), (64, torch.float16, "NHD"),
+                                             (128, torch.bfloat16, "NHD")])
+def test_core_matches_oracle(D, dtype, layout, causal, mode):
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 4, 2, 512, D, dtype, layout, seed=11, k_bias=1.0)
+    out, lse, qz = _run_core(q, k, v, layout, causal, mode, return_lse=True)
+    exp, exp_lse = _oracle(qz, layout, causal, mode, "per_thread", dtype)
+    _assert_close(out, exp, (D, dtype, layout, causal, mode))
+    assert float((lse.cpu() - exp_lse).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("N,Nkv", [(1, 1), (63, 63), (129, 129), (200, 200), (256, 256), (257, 257), (300, 1000),
+                                   (1000, 300), (777, 777)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_core_ragged_lengths(N, Nkv, causal):
+    cuda_or_fail()
+    q, k, v = make_qkv(2, 2, 2, N, 128, torch.float16, "HND", seed=N + Nkv, Nkv=Nkv, k_bias=0.5)
+    out, lse, qz = _run_core(q, k, v, "HND", causal, "fp32", return_lse=True)
+    exp, exp_lse = _oracle(qz, "HND", causal, "fp32", "per_thread", torch.float16)
+    _assert_close(out, exp, (N, Nkv, causal))
+    assert float((lse.cpu() - exp_lse).abs().max()) <= 2e-2
+
+
+def test_core_per_block_config1():
+    """BASELINE config 1: B=1, H=2, N=256, D=64, fp16, NHD, non-causal, smooth_k, fp32, per-block 128/64."""
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 2, 2, 256, 64, torch.float16, "NHD", seed=0)
+    out, _, qz = _run_core(q, k, v, "NHD", False, "fp32", gran="per_block")
+    exp, _ = _oracle(qz, "NHD", False, "fp32", "per_block", torch.float16)
+    _assert_close(out, exp, "config1")
+    q8, qs, k8, ks = O.quant_per_block(q.cpu(), k.cpu(), O.mean_k(k.cpu(), "NHD"), 128, 64, "NHD")
+    km_gpu_equal = torch.equal(O.mean_k(k.cpu(), "NHD"), __import__("sageattention").quant.mean_k(k, "NHD").cpu())
+    if km_gpu_equal:
+        assert torch.equal(qz[0].cpu(), q8) and torch.equal(qz[2].cpu(), k8)
+        assert torch.equal(qz[1].cpu(), qs) and torch.equal(qz[3].cpu(), ks)
+
+
+def test_core_sm_scale_argument():
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 2, 2, 384, 128, torch.float16, "HND", seed=3)
+    out, _, qz = _run_core(q, k, v, "HND", False, "fp32", sm_scale=0.05)
+    exp, _ = _oracle(qz, "HND", False, "fp32", "per_thread", torch.float16, sm_scale=0.05)
+    _assert_close(out, exp, "sm_scale")
+
+
+@pytest.mark.parametrize("mode,op", [("fp32", "qk_int8_sv_f16_accum_f32_attn"),
+                                      ("fp16+fp32", "qk_int8_sv_f16_accum_f16_attn_inst_buf"),
+                                      ("fp16", "qk_int8_sv_f16_accum_f16_attn")])
+@pytest.mark.parametrize("case", ["c2_like", "c3_like", "c4_like", "c5_like"])
+def test_core_matches_reference_cuda_kernel(case, mode, op):
+    """Same int8 tensors and scales into the reference's sm80 kernel (rebuilt for sm_100) and ours."""
+    cuda_or_fail()
+    ref = reference_ops()
+    assert ref is not None, "oracle/_ref/libsage_ref_sm80.so is missing: run make -C oracle"
+    if case == "c2_like":     # SD-style: D=64 fp16 HND, K offset N(0, 3^2)
+        args = dict(B=2, Hq=4, Hkv=4, N=1024, D=64, dtype=torch.float16, layout="HND", seed=1, k_bias=3.0)
+        causal = False
+    elif case == "c3_like":   # GQA prefill: D=128 bf16 NHD causal, 4 outlier channels x20
+        args = dict(B=1, Hq=8, Hkv=2, N=2048, D=128, dtype=torch.bfloat16, layout="NHD", seed=2, k_outliers=20.0)
+        causal = True
+    elif case == "c4_like":   # video DiT: ragged length, bf16 HND, K bias N(0, 2^2)
+        args = dict(B=1, Hq=2, Hkv=2, N=2320, D=128, dtype=torch.bfloat16, layout="HND", seed=3, k_bias=2.0)
+        causal = False
+    else:                     # long-context causal fp16
+        args = dict(B=1, Hq=4, Hkv=4, N=4096, D=128, dtype=torch.float16, layout="HND", seed=4)
+        causal = True
+    q, k, v = make_qkv(**args)
+    layout = args["layout"]
+    out, _, (q8, qs, k8, ks, v16) = _run_core(q, k, v, layout, causal, mode)
+    ref_out = torch.empty_like(q)
+    getattr(ref, op)(q8, k8, v16, ref_out, qs, ks, 0 if layout == "NHD" else 1, causal,
+                     q.size(-1) ** -0.5, *CFG, False)
+    torch.cuda.synchronize()
+    c = _assert_close(out, ref_out, (case, mode))
+    print(case, mode, c)
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+def test_sageattn_end_to_end_vs_sdpa(layout, dtype, causal):
+    """The reference's own acceptance test (tests/test_sageattn.py:52-61): fro-rel <= 0.02 and
+    max-abs <= 0.1 against SDPA-math, here for every head_dim incl. a padded one."""
+    import sageattention
+    cuda_or_fail()
+    for D in (64, 128, 80):
+        q, k, v = make_qkv(2, 4, 4, 1024, D, dtype, layout, seed=D)
+        for mode in ("fp32", "fp16+fp32", "fp16"):
+            for smooth_k in (True, False):
+                out = sageattention.sageattn(q, k, v, tensor_layout=layout, is_causal=causal,
+                                             pv_accum_dtype=mode, smooth_k=smooth_k)
+                exp, _ = O.sdpa_fp32(q.cpu(), k.cpu(), v.cpu(), layout, causal)
+                c = O.compare(out.cpu(), exp)
+                assert out.shape == q.shape and out.dtype == dtype
+                assert c["fro_rel"] <= 0.02 and c["max_abs"] <= 0.1, (D, mode, smooth_k, c)
+
+
+def test_sageattn_return_lse_gqa_causal():
+    import sageattention
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 8, 2, 1024, 128, torch.bfloat16, "NHD", seed=9, k_outliers=20.0)
+    out, lse = sageattention.sageattn(q, k, v, tensor_layout="NHD", is_causal=True, return_lse=True)
+    exp, exp_lse = O.sdpa_fp32(q.cpu(), k.cpu(), v.cpu(), "NHD", True)
+    assert lse.shape == (1, 8, 1024) and lse.dtype == torch.float32
+    # LSE of the quantised scores vs exact: int8 error on outlier-heavy K dominates
+    assert float((lse.cpu() - exp_lse).abs().max()) <= 0.25
+    assert O.compare(out.cpu(), exp)["fro_rel"] <= 0.1
+
+
+def test_sageattn_linearity_in_v_at_full_size():
+    """Size-independent property on a BASELINE-sized head (N = 32768, D = 128, causal): the output is
+    linear in V, and with V = const every row returns that constant."""
+    import sageattention
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 2, 2, 32768, 128, torch.float16, "HND", seed=4)
+    ones = torch.full_like(v, 0.5)
+    out = sageattention.sageattn(q, k, ones, is_causal=True, pv_accum_dtype="fp16+fp32")
+    assert float((out.float() - 0.5).abs().max()) <= 2e-3
+    o1 = sageattention.sageattn(q, k, v, is_causal=True)
+    o2 = sageattention.sageattn(q, k, 2 * v, is_causal=True)
+    assert float((o2.float() - 2 * o1.float()).abs().max()) <= 4e-3
+    # row 0 of a causal attention attends to key 0 only
+    assert torch.allclose(o1[:, :, 0].float(), v[:, :, 0].float(), atol=1e-3)
+
+
+def test_errors_are_loud():
+    import sageattention
+    from sageattention import _capi
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 2, 2, 64, 64, torch.float16, "HND", seed=1)
+    with pytest.raises(ValueError):
+        sageattention.sageattn(q, k, v.float())
+    with pytest.raises(ValueError):
+        sageattention.sageattn(q, k, v, tensor_layout="XYZ")
+    with pytest.raises(ValueError):
+        sageattention.sageattn(q, k, v, pv_accum_dtype="fp64")
+    with pytest.raises(ValueError):
+        sageattention.sageattn(q, k, v[:, :, :32])
+    with pytest.raises(_capi.SageB200Error):
+        sageattention.core._sageattn_configured(q, k, v, "HND", False, "fp32", True, False, False, (128, 32, 32, 32))

@@ -1,0 +1,126 @@
+"""CPU checks: the oracle against the reference's golden vectors, host-side logic, and the C-ABI
+library's exported symbols (no compute calls - there is no GPU here)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import golden_io as G
+from oracle import sage_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _same_bits(a: torch.Tensor, b: np.ndarray) -> bool:
+    return np.array_equal(a.numpy().view(np.uint32), b.view(np.uint32))
+
+
+@pytest.mark.parametrize("name", G.names())
+def test_oracle_quantisers_match_reference_bit_for_bit(name):
+    g = G.load(name)
+    r = g["raw"]
+    for cfg in G.PER_THREAD_CONFIGS:
+        tag = "pt_%d_%d_%d_%d" % cfg
+        q8, qs, k8, ks = O.quant_per_thread(g["q"], g["k"], g["km"], cfg[0], cfg[2], cfg[1], cfg[3], g["layout"])
+        assert _same_bits(qs, r[tag + "_qs"]) and _same_bits(ks, r[tag + "_ks"])
+        assert qs.shape == r[tag + "_qs"].shape and ks.shape == r[tag + "_ks"].shape
+        if tag + "_q8" in r:
+            assert np.array_equal(q8.numpy(), r[tag + "_q8"]) and np.array_equal(k8.numpy(), r[tag + "_k8"])
+        assert [int(q8.long().sum()), int((q8.long() ** 2).sum())] == list(r[tag + "_q8sum"])
+        assert [int(k8.long().sum()), int((k8.long() ** 2).sum())] == list(r[tag + "_k8sum"])
+    q8, qs, k8, ks = O.quant_per_block(g["q"], g["k"], g["km"], 128, 64, g["layout"])
+    assert _same_bits(qs, r["pb_128_64_qs"]) and _same_bits(ks, r["pb_128_64_ks"])
+    assert np.array_equal(q8.numpy(), r["pb_128_64_q8"]) and np.array_equal(k8.numpy(), r["pb_128_64_k8"])
+
+
+@pytest.mark.parametrize("name", G.names())
+def test_oracle_mean_matches_torch_mean_of_fixture(name):
+    g = G.load(name)
+    if g["km"] is None:
+        pytest.skip("fixture without smoothing")
+    assert torch.equal(O.mean_k(g["k"], g["layout"]), g["km"])
+
+
+@pytest.mark.parametrize("name", [n for n in G.names() if "tri_o_bits" in G.load(n)["raw"]])
+@pytest.mark.parametrize("causal", [False, True])
+def test_oracle_attention_matches_reference_triton_kernel(name, causal):
+    g = G.load(name)
+    r = g["raw"]
+    sfx = "_causal" if causal else ""
+    q8 = torch.from_numpy(r["pb_128_64_q8"])
+    k8 = torch.from_numpy(r["pb_128_64_k8"])
+    qs = torch.from_numpy(r["pb_128_64_qs"])
+    ks = torch.from_numpy(r["pb_128_64_ks"])
+    o, lse = O.attend(q8, k8, g["v"].half(), qs, ks, g["layout"], causal, None, "fp32", "per_block",
+                      128, 32, 64, 64, g["dtype"], True)
+    ref = G.from_bits(r["tri_o_bits" + sfx], g["dtype"])
+    c = O.compare(o, ref)
+    assert c["cos"] >= 0.99999 and c["max_abs"] <= 2e-3, c
+    assert float((lse - torch.from_numpy(r["tri_lse" + sfx])).abs().max()) <= 1e-3
+
+
+def test_oracle_end_to_end_close_to_fp32_attention():
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(1, 2, 300, 64, generator=g).half()
+    k = (torch.randn(1, 2, 300, 64, generator=g) + 2.0).half()
+    v = torch.randn(1, 2, 300, 64, generator=g).half()
+    for causal in (False, True):
+        for mode in ("fp32", "fp16+fp32", "fp16"):
+            o, lse = O.sageattn(q, k, v, "HND", causal, mode, True, True)
+            ref, ref_lse = O.sdpa_fp32(q, k, v, "HND", causal)
+            c = O.compare(o, ref)
+            assert c["cos"] > 0.999 and c["max_abs"] < 0.05, (causal, mode, c)
+            assert float((lse - ref_lse).abs().max()) < 0.05
+
+
+def test_header_symbols_are_exported():
+    hdr = open(os.path.join(ROOT, "include", "sage_b200.h")).read()
+    declared = sorted(set(re.findall(r"\b(sage_b200_[a-z0-9_]+)\s*\(", hdr)))
+    assert len(declared) >= 7
+    from sageattention import _capi
+    lib = _capi.lib()
+    for sym in declared:
+        assert hasattr(lib, sym), sym
+    assert set(declared) == set(_capi.EXPORTS)
+    assert lib.sage_b200_version() == 100
+
+
+def test_argument_errors_do_not_need_a_gpu():
+    from sageattention import _capi
+    lib = _capi.lib()
+    st = (ctypes.c_int64 * 3)(0, 0, 0)
+    rc = lib.sage_b200_quant_int8(0, 0, 0, 0, 0, 1, 1, 16, 64, st, st, 128, 32, 0, 0, 0)
+    assert rc == -1 and b"null pointer" in lib.sage_b200_last_error()
+    rc = lib.sage_b200_mean_k(16, 16, 16, 0, 5, 1, 1, 16, 64, st, 0)
+    assert rc == -1 and b"dtype" in lib.sage_b200_last_error()
+    assert lib.sage_b200_mean_k_scratch_bytes(1, 64, 32768, 128) > 0
+    assert lib.sage_b200_mean_k_scratch_bytes(0, 64, 32768, 128) == 0
+
+
+def test_front_end_validation_matches_reference_errors():
+    import sageattention
+    from sageattention.core import _padded_head_dim, _sageattn_configured
+    q = torch.zeros(1, 2, 16, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="CUDA"):
+        sageattention.sageattn(q, q, q)
+    with pytest.raises(AssertionError):
+        sageattention.sageattn(q, q, q, attn_mask=torch.ones(1))
+    assert [_padded_head_dim(d) for d in (32, 64, 80, 128, 129, 256)] == [64, 64, 128, 128, 256, 256]
+    with pytest.raises(ValueError):
+        _padded_head_dim(257)
+    assert sageattention.sageattn is sageattention.sageattn_qk_int8_pv_fp16_cuda
+    for name in ("sageattn_qk_int8_pv_fp8_cuda_sm90", "sageattn_varlen"):
+        assert hasattr(sageattention, name)
+
+
+def test_tile_table_is_total_and_consistent():
+    from sageattention.tile_table import QK_CONFIGS, SUPPORTED_QK_CONFIGS, select_qk_config
+    for d in (64, 128, 256):
+        for causal in (False, True):
+            for acc in ("fp32", "fp16", "fp16+fp32"):
+                for n in (1, 1024, 1025, 75600, 131072, 10 ** 6):
+                    cfg = select_qk_config(d, causal, acc, n)
+                    assert cfg in SUPPORTED_QK_CONFIGS and cfg in QK_CONFIGS
