@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the SageAttention forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one full `sageattn` call (K mean, Q/K int8 quantisation, attention core) on synthetic
+inputs of the named workload.  Default workload: the long-context case the headline target is
+quoted on - B=1, H=64, N=32768, D=128, fp16, causal, pv_accum_dtype="fp16+fp32", HND - with the 64
+heads sharded over the ranks (strong scaling, no data-path collective).
+
+Prints ONE JSON line (rank 0).  `value` is effective attention TOPS, 4*B*H*N^2*D / t, over all
+ranks, inputs resident in HBM; `e2e` is the same metric through the host-buffer API with the
+host<->device copies inside the timed region; `roofline` describes the attention kernel (timed
+with CUDA events inside the same steps); `cpu_baseline` is the CPU restatement of the algorithm
+timed on a bounded sample.  With --impl reference only that CPU restatement is timed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "sageattention-autotune_b200"))
+sys.path.insert(0, ROOT)
+
+import torch
+
+WORKLOADS = {
+    # name: B, Hq, Hkv, N, D, dtype, causal, pv_accum, layout, seed
+    "c5_32k": dict(B=1, Hq=64, Hkv=64, N=32768, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
+    "c5_16k": dict(B=1, Hq=64, Hkv=64, N=16384, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
+    "c5_64k": dict(B=1, Hq=64, Hkv=64, N=65536, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
+    "c5_4k": dict(B=1, Hq=64, Hkv=64, N=4096, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
+    "c5_32k_fp32": dict(B=1, Hq=64, Hkv=64, N=32768, D=128, dtype="float16", causal=True, pv="fp32", layout="HND", seed=4),
+    "c2_sd": dict(B=16, Hq=10, Hkv=10, N=4096, D=64, dtype="float16", causal=False, pv="fp16+fp32", layout="HND", seed=1, k_bias=3.0),
+    "c3_gqa": dict(B=4, Hq=32, Hkv=8, N=8192, D=128, dtype="bfloat16", causal=True, pv="fp32", layout="NHD", seed=2, k_outliers=20.0),
+    "c4_dit": dict(B=1, Hq=24, Hkv=24, N=75600, D=128, dtype="bfloat16", causal=False, pv="fp32", layout="HND", seed=3, k_bias=2.0),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def literal_flops(w, heads):
+    return 4.0 * w["B"] * heads * w["N"] * w["N"] * w["D"]
+
+
+def make_inputs(w, kv_lo, kv_hi, device, pin=False):
+    """This rank's heads of the synthetic workload: N(0,1) values, optional per-channel K offset
+    or outlier channels, seeded per kv-head so that the data does not depend on the sharding."""
+    rep = w["Hq"] // w["Hkv"]
+    dt = getattr(torch, w["dtype"])
+    B, N, D = w["B"], w["N"], w["D"]
+    hkv = kv_hi - kv_lo
+
+    def shape(h):
+        return (B, h, N, D) if w["layout"] == "HND" else (B, N, h, D)
+    gen = torch.Generator(device=device).manual_seed(w["seed"] * 1000 + kv_lo)
+    q = torch.randn(shape(hkv * rep), generator=gen, device=device, dtype=torch.float32).to(dt)
+    k = torch.randn(shape(hkv), generator=gen, device=device, dtype=torch.float32)
+    v = torch.randn(shape(hkv), generator=gen, device=device, dtype=torch.float32).to(dt)
+    if w.get("k_bias"):
+        bshape = (1, hkv, 1, D) if w["layout"] == "HND" else (1, 1, hkv, D)
+        k = k + w["k_bias"] * torch.randn(bshape, generator=gen, device=device)
+    if w.get("k_outliers"):
+        for h in range(hkv):
+            ch = torch.randperm(D, generator=gen, device=device)[:4]
+            if w["layout"] == "HND":
+                k[:, h, :, ch] *= w["k_outliers"]
+            else:
+                k[:, :, h, ch] *= w["k_outliers"]
+    return q, k.to(dt), v
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(w, seconds_hint=20.0):
+    """CPU restatement of quantise-then-attend (oracle/), all host threads, on a bounded sample:
+    one head of the workload at its full sequence length when that stays near `seconds_hint`,
+    otherwise a shorter sequence."""
+    from oracle import sage_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n = w["N"]
+    est = 4.0 * n * n * w["D"] / 0.04e12 * (0.5 if w["causal"] else 1.0) * 2
+    while est > seconds_hint * 1.5 and n > 1024:
+        n //= 2
+        est /= 4
+    ws = dict(w, B=1, Hq=w["Hq"] // w["Hkv"], Hkv=1, N=n)
+    q, k, v = make_inputs(ws, 0, 1, "cpu")
+    t0 = time.perf_counter()
+    O.sageattn(q, k, v, w["layout"], w["causal"], w["pv"], True)
+    dt = time.perf_counter() - t0
+    tops = literal_flops(ws, ws["Hq"]) / dt / 1e12
+    sample = f"B=1, {ws['Hq']} q-head(s) on 1 kv-head, N={n}, D={w['D']}, same dtype/causal/pv mode; {dt:.1f} s"
+    return {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port", "sample": sample}
+
+
+def run_reference(args, w):
+    """--impl reference: the reference has no CPU implementation of this path (its kernels are CUDA
+    and Triton only), so the arm times the CPU restatement in oracle/ on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    total = args.warmup + args.steps
+    # keep the whole arm within a few minutes: each step is one bounded sample
+    hint = max(2.0, min(20.0, 150.0 / max(1, total)))
+    base = None
+    t_all = time.perf_counter()
+    for i in range(total):
+        base = cpu_baseline(w, seconds_hint=hint)
+        if i >= args.warmup:
+            vals.append(base["value"])
+    wall = time.perf_counter() - t_all
+    value = statistics.mean(vals)
+    base["value"] = value
+    line = {"impl": "reference", "metric": "effective attention TOPS (4*B*H*N^2*D/t)", "value": value, "unit": "TOPS",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * wall / total, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8 QK^T + fp16 PV (fp32 CPU emulation)", "data": "synthetic",
+            "config": {"workload": args.workload, **{k: w[k] for k in ("B", "Hq", "Hkv", "N", "D", "causal", "pv", "layout")},
+                       "note": "CPU restatement (oracle/) on host cores; each step is the bounded sample in cpu_baseline.sample"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c5_32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--gather", action="store_true", help="also time the NCCL all-gather of the output")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    import torch.distributed as dist
+    import sageattention
+    from sageattention import core as sa_core
+    from sageattention.host import sageattn_host
+    from sageattention.parallel import local_heads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    (q_lo, q_hi), (kv_lo, kv_hi) = local_heads(w["Hq"], w["Hkv"], world, rank)
+    heads_local = q_hi - q_lo
+    q, k, v = make_inputs(w, kv_lo, kv_hi, dev)
+    kw = dict(tensor_layout=w["layout"], is_causal=w["causal"], pv_accum_dtype=w["pv"], smooth_k=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    out_holder = {}
+
+    def step():
+        out_holder["o"] = sageattention.sageattn(q, k, v, **kw) if heads_local > 0 else None
+
+    warmup = max(3, args.warmup)
+    sampler = ClockSampler(local_rank)
+    # ---- device-resident throughput, with per-kernel events collected over the timed steps
+    for _ in range(warmup):
+        step()
+    barrier()
+    sa_core._profile = []
+    sampler.start()
+    total_ms = timed(step, args.steps, 0)
+    clocks = sampler.stop()
+    prof, sa_core._profile = sa_core._profile, None
+    per_label = {}
+    for label, s, e in prof:
+        per_label.setdefault(label, []).append(s.elapsed_time(e))
+    kern_ms = {lab: sum(v_) / len(v_) for lab, v_ in per_label.items()}
+    ms_per_step = total_ms / args.steps
+    F_lit = literal_flops(w, w["Hq"])
+    F_exec_local = literal_flops(w, heads_local) * (0.5 if w["causal"] else 1.0)
+    value = F_lit / (ms_per_step * 1e-3) / 1e12
+
+    # ---- roofline of the attention kernel (this rank's launch)
+    pk = peaks()
+    attn_ms = kern_ms.get("attn")
+    achieved = F_exec_local / (attn_ms * 1e-3) / 1e12 if attn_ms else None
+    # half of the executed operations are int8 (2x the bf16 rate), half fp16: mixed peak = 4/3 * bf16
+    peak_mixed = pk["bf16_sustained"] * 4.0 / 3.0
+    roofline = {"bound": "tensor", "kernel": "sage_attn_fwd_kernel", "achieved": achieved, "peak": peak_mixed,
+                "unit": "TFLOP/s", "frac": (achieved / peak_mixed) if achieved else None, "traffic": None,
+                "peak_source": f"{pk['source']}: 4/3 x sustained dense bf16 ({pk['bf16_sustained']} TF/s); int8 counted at 2x bf16",
+                "frac_of_int8_peak_literal": (literal_flops(w, heads_local) / (attn_ms * 1e-3) / 1e12) / (2 * pk["bf16_sustained"]) if attn_ms else None,
+                "kernel_ms": kern_ms}
+    # quantisation front end against HBM: algorithmic bytes = 3 B per Q/K element + scales + mean, K counted once
+    els_q = w["B"] * heads_local * w["N"] * w["D"]
+    els_k = w["B"] * (kv_hi - kv_lo) * w["N"] * w["D"]
+    qbytes = 3.0 * (els_q + els_k)
+    front_ms = kern_ms.get("mean_k", 0.0) + kern_ms.get("quant_qk", 0.0)
+    roofline["quant"] = {"bound": "hbm", "achieved": qbytes / (front_ms * 1e-3) / 1e9 if front_ms else None,
+                         "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": (qbytes / (front_ms * 1e-3) / 1e9) / pk["hbm_gbs"] if front_ms else None}
+
+    # ---- optional all-gather of the output
+    gather_ms = None
+    if args.gather and world > 1:
+        full = torch.empty((world,) + tuple(out_holder["o"].shape), dtype=out_holder["o"].dtype, device=dev)
+
+        def step_gather():
+            step()
+            dist.all_gather_into_tensor(full, out_holder["o"].contiguous())
+        gather_ms = timed(step_gather, args.steps, 2) / args.steps
+
+    # ---- end to end from pinned host memory
+    e2e = None
+    if not args.no_e2e and heads_local > 0:
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+        hout = torch.empty(hq.shape, dtype=hq.dtype, pin_memory=True)
+
+        def step_host():
+            sageattn_host(hq, hk, hv, out=hout, device=dev, **kw)
+        e2e_steps = max(2, min(args.steps, 5))
+        e2e_ms = timed(step_host, e2e_steps, 1) / e2e_steps
+        e2e = {"value": F_lit / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in (hq, hk, hv))),
+               "d2h_bytes_per_step": int(hout.numel() * hout.element_size()),
+               "api": "sageattention.host.sageattn_host (pinned host tensors in, pinned host tensor out)"}
+
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        launches_per_step = 2 + 2 + 1 + (1 if w["dtype"] == "bfloat16" else 0)   # mean (2), quant q/k, attention, V cast
+        line = {"metric": "effective attention TOPS (4*B*H*N^2*D/t)", "value": value, "unit": "TOPS",
+                "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 QK^T + fp16 PV, fp32 softmax", "data": "synthetic",
+                "config": {"workload": args.workload, **{k_: w[k_] for k_ in ("B", "Hq", "Hkv", "N", "D", "causal", "pv", "layout")},
+                           "in_dtype": w["dtype"], "sharding": f"kv-heads over {world} rank(s), no collective in the timed region",
+                           "l2": "inputs (1.6 GB per step at N=32k) exceed the 126 MB L2; no flush needed"},
+                "executed_tops": value * (0.5 if w["causal"] else 1.0),
+                "clocks": clocks, "roofline": roofline, "e2e": e2e,
+                "gpu_launches": launches_per_step * args.steps,
+                "gather_ms_per_step": gather_ms}
+        if not args.no_cpu and world == 1:
+            line["cpu_baseline"] = cpu_baseline(w)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

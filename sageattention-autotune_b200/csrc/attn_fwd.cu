@@ -14,8 +14,10 @@
 //   warp  9     MMA issuer (one elected lane)
 //   warps 10-11 idle (they complete the third warpgroup so that setmaxnreg can be used)
 // Tensor memory (512 columns): per tile 128 columns for S (int32); P (fp16, two keys per
-// column) overwrites columns 0-63 of S, the fp16 per-block partial product of the
-// "fp16+fp32" mode uses columns 64.. of S; 128 more columns hold O.
+// column) overwrites columns 0-63 of S; 128 more columns hold O.  An fp16 accumulator occupies
+// one column per element (value in the low half), so the "fp16" mode keeps O as D such columns,
+// and the "fp16+fp32" mode computes each block's partial product 64 channels at a time into
+// columns 64-127 of S and folds it into the fp32 O before the next 64 channels are issued.
 // K/V blocks of 128 keys are shared by both tiles, so each byte of K and V is fetched once per
 // 256 query rows.
 //
@@ -254,18 +256,18 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
         if (!ok) break;
         ptx::tc_fence_after();
         if constexpr (kF16Acc) {
-          // O lives as packed fp16 pairs; the factor is rounded to fp16 as the reference does
-          const __half2 a2 = __float2half2_rn(alpha);
+          // O is fp16 (one value per column); the factor is rounded to fp16 as the reference does
+          // (update_mdo<..., true>, attn_utils.cuh:313-336)
+          const __half a16 = __float2half_rn(alpha);
 #pragma unroll
-          for (int c0 = 0; c0 < D / 2; c0 += 32) {
+          for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t o[32];
             ptx::tmem_ld32<0>(t_o + c0, o);
             ptx::tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              __half2 v = *reinterpret_cast<__half2*>(&o[i]);
-              v = __hmul2(v, a2);
-              o[i] = *reinterpret_cast<uint32_t*>(&v);
+              const __half v = __hmul(__ushort_as_half(static_cast<unsigned short>(o[i] & 0xffffu)), a16);
+              o[i] = __half_as_ushort(v);
             }
             ptx::tmem_st32<0>(t_o + c0, o);
           }
@@ -320,33 +322,34 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     ptx::mbar_arrive(bar_p_full);
 
     if constexpr (kInstBuf) {
-      // "fp16+fp32": this block's P.V was accumulated in fp16 from zero; fold it into the fp32 O
-      ok = wait_bar_warp(bar_pv_done, j & 1, abort_flag, 30 + tile);
-      if (!ok) break;
-      ptx::tc_fence_after();
+      // "fp16+fp32": this block's P.V is accumulated in fp16 from zero, 64 channels at a time, and
+      // folded into the fp32 O (compute_fp16_sv_permuted_inst_buf, attn_utils.cuh:447-518)
       const bool any_rescale = __any_sync(0xffffffffu, rescale);
+#pragma unroll 1
+      for (int ch = 0; ch < D / 64 && ok; ++ch) {
+        ok = wait_bar_warp(bar_pv_done, (j * (D / 64) + ch) & 1, abort_flag, 30 + tile);
+        if (!ok) break;
+        ptx::tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t t16[32];
-        uint32_t o[32];
-        // 32 fp32 columns of O pair with 16 packed columns of T; load 32 packed columns every second pass
-        ptx::tmem_ld32<0>(t_t + (c0 / 64) * 32, t16);
-        if (j > 0) ptx::tmem_ld32<0>(t_o + c0, o);
-        ptx::tmem_wait_ld();
-        const int half_sel = (c0 / 32) & 1;
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t t16[32];
+          uint32_t o[32];
+          ptx::tmem_ld32<0>(t_t + c0, t16);
+          if (j > 0) ptx::tmem_ld32<0>(t_o + ch * 64 + c0, o);
+          ptx::tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const uint32_t pk = t16[half_sel * 16 + i / 2];
-          const unsigned short hbits = static_cast<unsigned short>((i & 1) ? (pk >> 16) : (pk & 0xffffu));
-          float acc = (j > 0) ? __uint_as_float(o[i]) : 0.0f;
-          if (any_rescale) acc *= alpha;
-          o[i] = __float_as_uint(ptx::add_f32_f16(acc, hbits));
+          for (int i = 0; i < 32; ++i) {
+            float acc = (j > 0) ? __uint_as_float(o[i]) : 0.0f;
+            if (any_rescale) acc *= alpha;
+            o[i] = __float_as_uint(ptx::add_f32_f16(acc, static_cast<unsigned short>(t16[i] & 0xffffu)));
+          }
+          ptx::tmem_st32<0>(t_o + ch * 64 + c0, o);
         }
-        ptx::tmem_st32<0>(t_o + c0, o);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_s_free);
       }
-      ptx::tmem_wait_st();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bar_s_free);
+      if (!ok) break;
     }
   }
 
@@ -362,23 +365,23 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     unsigned short* orow = static_cast<unsigned short*>(p.out) + b * p.os_b + h * p.os_h + q_row * p.os_n;
     if constexpr (kF16Acc) {
 #pragma unroll
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+      for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t o[32];
         ptx::tmem_ld32<0>(t_o + c0, o);
         ptx::tmem_wait_ld();
-        uint32_t w[32];
+        uint32_t w[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const __half2 v = *reinterpret_cast<const __half2*>(&o[i]);
-          // normalise in fp32, round to fp16 (the accumulator type), then to the output type
-          const float lo = __half2float(__float2half_rn(__low2float(v) * inv));
-          const float hi = __half2float(__float2half_rn(__high2float(v) * inv));
-          w[i] = pack_out<OUT_DTYPE>(lo, hi);
+        for (int i = 0; i < 16; ++i) {
+          // normalise in fp32, round to fp16 (the accumulator type, normalize_d in attn_utils.cuh:565-567),
+          // then to the output type
+          const float lo = __half2float(__ushort_as_half(static_cast<unsigned short>(o[2 * i] & 0xffffu)));
+          const float hi = __half2float(__ushort_as_half(static_cast<unsigned short>(o[2 * i + 1] & 0xffffu)));
+          w[i] = pack_out<OUT_DTYPE>(__half2float(__float2half_rn(lo * inv)), __half2float(__float2half_rn(hi * inv)));
         }
         if (store) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<uint4*>(orow + 2 * c0 + 2 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<uint4*>(orow + c0 + 2 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
         }
       }
     } else {
@@ -516,7 +519,8 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t k_smem = smem_base + Plan::kKOff;
       const uint32_t v_smem = smem_base + Plan::kVOff;
       const uint32_t idq = idesc_qk();
-      const uint32_t idp = idesc_pv<D, kF16Acc || kInstBuf>();
+      const uint32_t idp = idesc_pv<D, kF16Acc>();
+      const uint32_t idp_chunk = idesc_pv<64, true>();
 
       auto issue_qk = [&](int t, int stage) {
         const uint32_t d_t = tmem_base + t * 256;
@@ -532,13 +536,24 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
       };
       auto issue_pv = [&](int t, int stage, bool accumulate) {
-        const uint32_t d_t = tmem_base + t * 256 + (kInstBuf ? 64 : 128);
+        const uint32_t d_t = tmem_base + t * 256 + 128;
         const uint32_t a_t = tmem_base + t * 256;
 #pragma unroll
         for (int s = 0; s < kBlockKV / 16; ++s) {
           // 16 keys per instruction: 8 packed columns of P, 16 rows (2 KB) of every V panel
           const uint64_t db = desc_mnmajor(v_smem + stage * Plan::kVBytes + s * 2048, kBlockKV * 128);
           ptx::mma_f16_ts(d_t, a_t + s * 8, db, idp, (accumulate || s != 0) ? 1u : 0u);
+        }
+      };
+      // "fp16+fp32": one 64-channel panel of V at a time into the fp16 scratch columns
+      auto issue_pv_chunk = [&](int t, int stage, int ch) {
+        const uint32_t d_t = tmem_base + t * 256 + 64;
+        const uint32_t a_t = tmem_base + t * 256;
+#pragma unroll
+        for (int s = 0; s < kBlockKV / 16; ++s) {
+          const uint64_t db = desc_mnmajor(v_smem + stage * Plan::kVBytes + ch * (kBlockKV * 128) + s * 2048,
+                                           kBlockKV * 128);
+          ptx::mma_f16_ts(d_t, a_t + s * 8, db, idp_chunk, s != 0 ? 1u : 0u);
         }
       };
 
@@ -580,18 +595,22 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
           }
         } else {
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (j < n_blk[t]) {
-              ok = wait_bar(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
-              if (!ok) break;
-              ptx::tc_fence_after();
-              issue_pv(t, vs, false);
-              ptx::tc_commit(bars + 8 * (kBarPvDone + t));
+          constexpr int kChunks = D / 64;
+          for (int ch = 0; ch < kChunks && ok; ++ch) {
+            for (int t = 0; t < 2 && ok; ++t) {
+              if (j < n_blk[t]) {
+                if (ch == 0) ok = wait_bar(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
+                else ok = wait_bar(bars + 8 * (kBarSFree + t), (j * kChunks + ch - 1) & 1, abort_flag, 66 + t);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                issue_pv_chunk(t, vs, ch);
+                ptx::tc_commit(bars + 8 * (kBarPvDone + t));
+              }
             }
           }
           for (int t = 0; t < 2 && ok; ++t) {
             if (nxt < n_blk[t]) {
-              ok = wait_bar(bars + 8 * (kBarSFree + t), j & 1, abort_flag, 66 + t);
+              ok = wait_bar(bars + 8 * (kBarSFree + t), (j * kChunks + kChunks - 1) & 1, abort_flag, 68 + t);
               if (!ok) break;
               ptx::tc_fence_after();
               issue_qk(t, ks);

@@ -28,6 +28,29 @@ if DEFAULT_PV_ACCUM_DTYPE not in ("fp32", "fp16", "fp16+fp32"):
 _PV_CODE = {"fp32": C.PV_F32, "fp16": C.PV_F16, "fp16+fp32": C.PV_F16_F32}
 
 
+# When set to a list, (label, start_event, end_event) is appended around each group of kernel
+# launches, so that callers (the benchmark) can time the attention kernel alone inside a full call.
+_profile = None
+
+
+class _Timed:
+    def __init__(self, label):
+        self.label = label
+
+    def __enter__(self):
+        if _profile is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _profile is not None:
+            self.end.record()
+            _profile.append((self.label, self.start, self.end))
+        return False
+
+
 def _check_status_enabled() -> bool:
     return os.getenv("SAGE_B200_CHECK", "0").lower() in ("1", "true", "yes", "on")
 
@@ -131,17 +154,21 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         return t if (t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
     q, k, v = _aligned(q), _aligned(k), _aligned(v)
 
-    km = mean_k(k, tensor_layout) if smooth_k else None
+    with _Timed("mean_k"):
+        km = mean_k(k, tensor_layout) if smooth_k else None
     blk_q, blk_k, warp_q, warp_k = qk_config
-    if qk_quant_gran == "per_thread":
-        q_int8, q_scale, k_int8, k_scale = per_thread_int8(q, k, km, blk_q, warp_q, blk_k, warp_k, tensor_layout)
-    else:
-        q_int8, q_scale, k_int8, k_scale = per_block_int8(q, k, km, blk_q, blk_k, tensor_layout)
+    with _Timed("quant_qk"):
+        if qk_quant_gran == "per_thread":
+            q_int8, q_scale, k_int8, k_scale = per_thread_int8(q, k, km, blk_q, warp_q, blk_k, warp_k, tensor_layout)
+        else:
+            q_int8, q_scale, k_int8, k_scale = per_block_int8(q, k, km, blk_q, blk_k, tensor_layout)
+    with _Timed("cast_v"):
+        v_fp16 = cast_v_fp16(v, tensor_layout)
 
     output = torch.empty(q.size(), dtype=dtype, device=q.device)
-    lse = attn_fwd_quantized(q_int8, k_int8, cast_v_fp16(v, tensor_layout), output, q_scale, k_scale,
-                             tensor_layout, is_causal, sm_scale, qk_config, pv_accum_dtype, return_lse,
-                             qk_quant_gran)
+    with _Timed("attn"):
+        lse = attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_layout, is_causal,
+                                 sm_scale, qk_config, pv_accum_dtype, return_lse, qk_quant_gran)
     output = output[..., :head_dim]
     if not return_lse:
         return output

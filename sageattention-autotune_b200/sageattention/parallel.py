@@ -1,0 +1,74 @@
+"""Head sharding across the GPUs of one node.
+
+The reference is single-GPU.  Every (batch, kv-head) pair of the forward path is independent - the
+K mean, the quantisation and the attention core never look across heads - so the natural
+multi-GPU form is one process per GPU, each running the unchanged single-GPU pipeline on a
+contiguous range of kv-heads together with the query heads that share them (GQA groups are never
+split).  No kernel touches another GPU's memory.  NCCL is used for exactly one thing: an
+all-gather of the output (and LSE) when the caller asks for the whole tensor on every rank.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_units: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous [begin, end) of `n_units` owned by `rank`: ceil(n/world) per rank, last ranks may
+    own fewer (or none)."""
+    if n_units < 0 or world_size <= 0 or not 0 <= rank < world_size:
+        raise ValueError("bad shard request")
+    per = -(-n_units // world_size)
+    lo = min(n_units, rank * per)
+    return lo, min(n_units, lo + per)
+
+
+def local_heads(num_q_heads: int, num_kv_heads: int, world_size: int, rank: int):
+    """(q_head_range, kv_head_range) for this rank; kv-heads are the sharded unit."""
+    if num_q_heads % num_kv_heads:
+        raise ValueError("num_qo_heads must be divisible by num_kv_heads")
+    rep = num_q_heads // num_kv_heads
+    lo, hi = shard_range(num_kv_heads, world_size, rank)
+    return (lo * rep, hi * rep), (lo, hi)
+
+
+def slice_heads(t: torch.Tensor, tensor_layout: str, lo: int, hi: int) -> torch.Tensor:
+    return t[:, lo:hi] if tensor_layout == "HND" else t[:, :, lo:hi]
+
+
+def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout: str = "HND",
+                     group: Optional[dist.ProcessGroup] = None, gather: bool = True,
+                     attn_fn: Optional[Callable] = None, **kwargs):
+    """Run attention on this rank's heads; optionally all-gather the full output.
+
+    q_local/k_local/v_local hold only this rank's heads (as produced by `local_heads` +
+    `slice_heads`).  With gather=True every rank returns the output for all `num_q_heads` heads,
+    in the input layout; with gather=False the local result is returned untouched and no
+    collective is issued.  `attn_fn` defaults to sageattention.sageattn."""
+    if attn_fn is None:
+        from .core import sageattn as attn_fn
+    res = attn_fn(q_local, k_local, v_local, tensor_layout=tensor_layout, **kwargs)
+    if not gather or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return res
+    world = dist.get_world_size(group)
+    want_lse = isinstance(res, tuple)
+    out, lse = res if want_lse else (res, None)
+    h_dim = 1 if tensor_layout == "HND" else 2
+    per = -(-num_q_heads // world)
+
+    def gather_heads(x, dim):
+        # equal-sized slots of `per` heads, head dim moved to the front so that each rank's
+        # contribution is one contiguous block of the gathered buffer
+        xt = x.movedim(dim, 0)
+        slot = torch.zeros((per,) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
+        slot[: xt.size(0)] = xt
+        full = torch.empty((world * per,) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(full, slot.contiguous(), group=group)
+        return full[:num_q_heads].movedim(0, dim)
+
+    out_full = gather_heads(out, h_dim)
+    if want_lse:
+        return out_full, gather_heads(lse, 1)
+    return out_full

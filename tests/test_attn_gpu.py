@@ -39,8 +39,17 @@ def _oracle(quantised, layout, causal, mode, gran, dtype, sm_scale=None):
 
 
 def _assert_close(got, exp, what):
-    c = O.compare(got.cpu(), exp.cpu())
-    assert c["cos"] >= COS_MIN and c["max_abs"] <= MAX_ABS, (what, c)
+    """cos >= 0.9995 and max-abs <= 2e-2.  For bf16 outputs one unit in the last place is 0.03125
+    once |o| >= 4 (early causal rows see few keys and reach such values), so there the bound is
+    one bf16 ulp of the expected value: a single rounding flip, nothing more."""
+    got, exp = got.cpu(), exp.cpu()
+    c = O.compare(got, exp)
+    bound = torch.full_like(exp.float(), MAX_ABS)
+    if exp.dtype == torch.bfloat16:
+        ulp = torch.exp2(torch.floor(torch.log2(exp.float().abs().clamp_min(1e-30))) - 7)
+        bound = torch.maximum(bound, ulp)
+    worst = float(((got.float() - exp.float()).abs() - bound).max())
+    assert c["cos"] >= COS_MIN and worst <= 0.0, (what, c, worst)
     return c
 
 
@@ -76,9 +85,9 @@ def test_core_per_block_config1():
     out, _, qz = _run_core(q, k, v, "NHD", False, "fp32", gran="per_block")
     exp, _ = _oracle(qz, "NHD", False, "fp32", "per_block", torch.float16)
     _assert_close(out, exp, "config1")
+    from sageattention import quant
     q8, qs, k8, ks = O.quant_per_block(q.cpu(), k.cpu(), O.mean_k(k.cpu(), "NHD"), 128, 64, "NHD")
-    km_gpu_equal = torch.equal(O.mean_k(k.cpu(), "NHD"), __import__("sageattention").quant.mean_k(k, "NHD").cpu())
-    if km_gpu_equal:
+    if torch.equal(O.mean_k(k.cpu(), "NHD"), quant.mean_k(k, "NHD").cpu()):
         assert torch.equal(qz[0].cpu(), q8) and torch.equal(qz[2].cpu(), k8)
         assert torch.equal(qz[1].cpu(), qs) and torch.equal(qz[3].cpu(), ks)
 
@@ -144,15 +153,21 @@ def test_sageattn_end_to_end_vs_sdpa(layout, dtype, causal):
 
 
 def test_sageattn_return_lse_gqa_causal():
+    """BASELINE config 3 in small: GQA, causal, bf16, NHD, outlier channels, return_lse.  The LSE
+    (natural log, with the smooth-k correction added back) is checked against the CPU oracle run
+    through the same pipeline, and loosely against exact attention (int8 error on outlier-heavy K
+    dominates that distance)."""
     import sageattention
     cuda_or_fail()
     q, k, v = make_qkv(1, 8, 2, 1024, 128, torch.bfloat16, "NHD", seed=9, k_outliers=20.0)
     out, lse = sageattention.sageattn(q, k, v, tensor_layout="NHD", is_causal=True, return_lse=True)
-    exp, exp_lse = O.sdpa_fp32(q.cpu(), k.cpu(), v.cpu(), "NHD", True)
     assert lse.shape == (1, 8, 1024) and lse.dtype == torch.float32
-    # LSE of the quantised scores vs exact: int8 error on outlier-heavy K dominates
-    assert float((lse.cpu() - exp_lse).abs().max()) <= 0.25
-    assert O.compare(out.cpu(), exp)["fro_rel"] <= 0.1
+    o_exp, lse_exp = O.sageattn(q.cpu(), k.cpu(), v.cpu(), "NHD", True, "fp32", True, True)
+    assert float((lse.cpu() - lse_exp).abs().max()) <= 2e-2
+    _assert_close(out, o_exp, "c3 small vs oracle")
+    exact, exact_lse = O.sdpa_fp32(q.cpu(), k.cpu(), v.cpu(), "NHD", True)
+    assert float((lse.cpu() - exact_lse).abs().max()) <= 1.0
+    assert O.compare(out.cpu(), exact)["fro_rel"] <= 0.1
 
 
 def test_sageattn_linearity_in_v_at_full_size():

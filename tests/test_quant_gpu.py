@@ -136,6 +136,7 @@ def test_quant_idempotent_properties_at_full_size():
     sc = qs.view(B, H, N // 32, 1, 8, 1).expand(B, H, N // 32, 4, 8, 1).reshape(B, H, N, 1)
     err = (q8.float() * sc - q.float()).abs()
     assert bool((err <= 0.5 * sc * 1.0001 + 1e-6).all())
-    amax = q.float().abs().view(B, H, N // 32, 4, 8, D).amax(dim=(3, 5))
-    assert torch.equal(qs.view(B, H, N // 32, 8), amax / 127.0 + 1e-7)
+    # evaluated on the CPU: torch's CUDA division by a scalar multiplies by the reciprocal
+    amax = q.float().abs().view(B, H, N // 32, 4, 8, D).amax(dim=(3, 5)).cpu()
+    assert torch.equal(qs.view(B, H, N // 32, 8).cpu(), amax / 127.0 + 1e-7)
     assert int(q8.abs().max()) == 127
