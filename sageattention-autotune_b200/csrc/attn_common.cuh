@@ -1,0 +1,113 @@
+// Shared pieces of the attention kernels: launch parameters, bounded mbarrier waits, UMMA
+// descriptors and the optional debug trace.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace sage {
+
+constexpr int kTileQ = 128;
+constexpr int kBlockKV = 128;
+constexpr int kAttnThreads = 384;
+constexpr int kKStages = 3;
+constexpr int kVStages = 3;
+constexpr long long kWaitCycles = 4000000000LL;   // about two seconds of SM clock
+constexpr float kLog2e = 1.44269504088896340736f;
+constexpr float kMagicF = 12582912.0f;            // 1.5 * 2^23
+constexpr uint32_t kMagicI = 0x4B400000u;
+constexpr float kLazyRescale = 8.0f;              // fp32 accumulators: rescale O only if max grew by 2^8
+
+struct AttnParams {
+  const float* q_scale;
+  const float* k_scale;
+  void* out;
+  float* lse;
+  int32_t* status;
+  int len_q, len_kv, heads_q, heads_kv;
+  int q_groups, k_groups;       // scale entries per head
+  int warp_q;                    // WARPQ (per-thread) or BLKQ (per-block)
+  int gran;
+  int causal;
+  float scale_log2;              // sm_scale * log2(e)
+  int64_t os_b, os_h, os_n;
+#ifdef SAGE_TRACE
+  long long* trace;              // debug builds only: per-role event timestamps of one CTA
+#endif
+};
+
+#ifdef SAGE_TRACE
+// role r writes (event << 56 | j << 40 | clock) into trace[r * 8192 + n]; slot 0 holds n
+#define SAGE_TR(role, ev, j)                                                                         \
+  do {                                                                                               \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {               \
+      long long* base_ = p.trace + (role) * 8192;                                                    \
+      long long n_ = base_[0];                                                                       \
+      if (n_ < 8190) {                                                                               \
+        base_[1 + n_] = (static_cast<long long>(ev) << 56) | (static_cast<long long>(j) << 40) |     \
+                        (clock64() & 0xffffffffffLL);                                                \
+        base_[0] = n_ + 1;                                                                           \
+      }                                                                                              \
+    }                                                                                                \
+  } while (0)
+#else
+#define SAGE_TR(role, ev, j) do {} while (0)
+#endif
+
+// Bounded mbarrier wait.  Returns false if the CTA is aborting.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      atomicCAS(const_cast<int*>(abort_flag), 0, code);
+      return false;
+    }
+  }
+}
+
+// Same, for code that goes on to warp-collective tcgen05.ld/st: the verdict is made warp-uniform.
+__device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, code));
+}
+
+// K-major operand tile whose rows are ROW_BYTES wide (64 -> 64-byte swizzle, 128 -> 128-byte swizzle)
+template <int ROW_BYTES>
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
+  constexpr uint64_t layout = (ROW_BYTES == 128) ? 2 : 4;
+  constexpr uint64_t sbo = (8 * ROW_BYTES) >> 4;            // 8 rows
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (sbo << 32) |
+         (uint64_t(1) << 46) | (layout << 61);
+}
+// MN-major operand (V as [keys][64 channels] panels, 128-byte swizzle): 8 keys = 1024 bytes apart,
+// next 64-channel panel `panel_bytes` apart
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr, uint32_t panel_bytes) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(panel_bytes >> 4) << 16) |
+         (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+__host__ __device__ constexpr uint32_t idesc_qk() {
+  // int8 x int8 -> int32, both K-major, M = 128, N = 128
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((kBlockKV >> 3) << 17) | ((kTileQ >> 4) << 24);
+}
+template <int D, bool F16_ACC>
+__host__ __device__ constexpr uint32_t idesc_pv() {
+  // fp16 x fp16 -> fp32 (or fp16), A from tensor memory, B MN-major, M = 128, N = D
+  return ((F16_ACC ? 0u : 1u) << 4) | (0u << 7) | (0u << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) |
+         ((kTileQ >> 4) << 24);
+}
+
+template <int OUT_DTYPE>
+__device__ __forceinline__ uint32_t pack_out(float lo, float hi) {
+  if constexpr (OUT_DTYPE == SAGE_B200_BF16) return ptx::pack_bf16x2(lo, hi);
+  else return ptx::pack_f16x2(lo, hi);
+}
+
+
+}  // namespace sage

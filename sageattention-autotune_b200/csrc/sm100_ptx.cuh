@@ -209,10 +209,41 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
-// fp32 accumulator + fp16 addend in one instruction
-__device__ __forceinline__ float add_f32_f16(float acc, unsigned short h) {
+// fp32 accumulator + the fp16 value held in the low half of a 32-bit register, one instruction
+__device__ __forceinline__ float add_f32_f16lo(float acc, uint32_t packed) {
   float r;
-  asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(r) : "h"(h), "f"(acc));
+  asm("{\n"
+      " .reg .b16 lo, hi;\n"
+      " mov.b32 {lo, hi}, %1;\n"
+      " add.rn.f32.f16 %0, lo, %2;\n"
+      "}"
+      : "=f"(r)
+      : "r"(packed), "f"(acc));
+  return r;
+}
+// three-input maximum
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// packed pairs of fp32 (sm_100: one issue slot for two lanes)
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
 
