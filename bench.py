@@ -37,6 +37,7 @@ WORKLOADS = {
     "c5_16k": dict(B=1, Hq=64, Hkv=64, N=16384, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
     "c5_64k": dict(B=1, Hq=64, Hkv=64, N=65536, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
     "c5_4k": dict(B=1, Hq=64, Hkv=64, N=4096, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
+    "c5_8k_fp32": dict(B=1, Hq=32, Hkv=32, N=8192, D=128, dtype="float16", causal=False, pv="fp32", layout="HND", seed=4),
     "c5_32k_fp32": dict(B=1, Hq=64, Hkv=64, N=32768, D=128, dtype="float16", causal=True, pv="fp32", layout="HND", seed=4),
     "c2_sd": dict(B=16, Hq=10, Hkv=10, N=4096, D=64, dtype="float16", causal=False, pv="fp16+fp32", layout="HND", seed=1, k_bias=3.0),
     "c3_gqa": dict(B=4, Hq=32, Hkv=8, N=8192, D=128, dtype="bfloat16", causal=True, pv="fp32", layout="NHD", seed=2, k_outliers=20.0),

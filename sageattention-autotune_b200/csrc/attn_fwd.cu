@@ -55,11 +55,13 @@ static int make_map(CUtensorMap* map, const void* base, int elem_bytes, int batc
 template <int D, int PV_MODE, int OUT_DTYPE>
 static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                        dim3 grid, cudaStream_t stream) {
-  // "fp16+fp32" keeps its per-block fp16 scratch in tensor memory next to S and runs the coupled
-  // kernel; the other modes run the decoupled one.  SAGE_B200_KERNEL=coupled forces the former.
+  // Two pipelines exist.  The coupled one (128-key steps, one score buffer per tile) is the default:
+  // it measures fastest on B200 because the softmax warps are bound by instruction issue, and it
+  // pays the fixed per-step cost half as often.  "fp16+fp32" needs its spare score columns and always
+  // runs it.  SAGE_B200_KERNEL=decoupled selects the double-buffered 64-key pipeline for the others.
   static const bool force_v1 = [] {
     const char* e = getenv("SAGE_B200_KERNEL");
-    return e != nullptr && e[0] == 'c';
+    return !(e != nullptr && e[0] == 'd');
   }();
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
   int smem;

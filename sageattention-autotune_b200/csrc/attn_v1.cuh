@@ -460,8 +460,14 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 0) &&
                           !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 1); ++i) {}
       }
-    } else if (warp == 9 && lane == 0) {
+    } else if (warp == 9) {
       // ---------------- MMA issuer ----------------
+      // The whole warp runs this loop and one elected lane issues: operands that are computed in
+      // converged code stay in uniform registers, which tcgen05.mma and tcgen05.commit read directly.
+      auto commit = [&](uint32_t bar) {
+        if (ptx::elect_one()) ptx::tc_commit(bar);
+        __syncwarp();
+      };
       constexpr int kRowBytesQK = (D == 64) ? 64 : 128;
       constexpr int kPanelsQK = D / kRowBytesQK;              // 1 (2 for D = 256)
       constexpr int kStepsPerPanel = kRowBytesQK / 32;        // int8: 32 bytes of K per instruction
@@ -482,74 +488,83 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t d_t = tmem_base + t * 256;
         const uint64_t da0 = q_desc0 + static_cast<uint64_t>((t * Plan::kQBytes) >> 4);
         const uint64_t db0 = k_desc0 + static_cast<uint64_t>((stage * Plan::kKBytes) >> 4);
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int pn = 0; pn < kPanelsQK; ++pn) {
+          for (int pn = 0; pn < kPanelsQK; ++pn) {
 #pragma unroll
-          for (int s = 0; s < kStepsPerPanel; ++s) {
-            const uint64_t off = static_cast<uint64_t>((pn * (kTileQ * kRowBytesQK) + s * 32) >> 4);
-            ptx::mma_i8_ss(d_t, da0 + off, db0 + off, idq, (pn | s) != 0);
+            for (int s = 0; s < kStepsPerPanel; ++s) {
+              const uint64_t off = static_cast<uint64_t>((pn * (kTileQ * kRowBytesQK) + s * 32) >> 4);
+              ptx::mma_i8_ss(d_t, da0 + off, db0 + off, idq, (pn | s) != 0);
+            }
           }
         }
+        __syncwarp();
       };
       auto issue_pv = [&](int t, int stage, bool accumulate) {
         const uint32_t d_t = tmem_base + t * 256 + 128;
         const uint32_t a_t = tmem_base + t * 256;
         const uint64_t db0 = v_desc0 + static_cast<uint64_t>((stage * Plan::kVBytes) >> 4);
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int s = 0; s < kBlockKV / 16; ++s) {
-          // 16 keys per instruction: 8 packed columns of P, 16 rows (2 KB) of every V panel
-          ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 2048) >> 4), idp,
-                          (accumulate || s != 0) ? 1u : 0u);
+          for (int s = 0; s < kBlockKV / 16; ++s) {
+            // 16 keys per instruction: 8 packed columns of P, 16 rows (2 KB) of every V panel
+            ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 2048) >> 4), idp,
+                            (accumulate || s != 0) ? 1u : 0u);
+          }
         }
+        __syncwarp();
       };
       // "fp16+fp32": one 64-channel panel of V at a time into the fp16 scratch columns
       auto issue_pv_chunk = [&](int t, int stage, int ch) {
         const uint32_t d_t = tmem_base + t * 256 + 64;
         const uint32_t a_t = tmem_base + t * 256;
         const uint64_t db0 = v_desc0 + static_cast<uint64_t>((stage * Plan::kVBytes + ch * (kBlockKV * 128)) >> 4);
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int s = 0; s < kBlockKV / 16; ++s)
-          ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 2048) >> 4), idp_chunk, s != 0 ? 1u : 0u);
+          for (int s = 0; s < kBlockKV / 16; ++s)
+            ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 2048) >> 4), idp_chunk, s != 0 ? 1u : 0u);
+        }
+        __syncwarp();
       };
 
-      bool ok = wait_bar(bars + 8 * kBarQFull, 0, abort_flag, 60);
-      if (ok && n_max > 0) ok = wait_bar(bars + 8 * (kBarKFull + 0), 0, abort_flag, 61);
+      bool ok = wait_bar_warp(bars + 8 * kBarQFull, 0, abort_flag, 60);
+      if (ok && n_max > 0) ok = wait_bar_warp(bars + 8 * (kBarKFull + 0), 0, abort_flag, 61);
       if (ok && n_max > 0) {
         ptx::tc_fence_after();
         for (int t = 0; t < 2; ++t) {
           if (n_blk[t] > 0) {
             issue_qk(t, 0);
-            ptx::tc_commit(bars + 8 * (kBarSFull + t));
+            commit(bars + 8 * (kBarSFull + t));
           }
         }
-        ptx::tc_commit(bars + 8 * (kBarKEmpty + 0));
+        commit(bars + 8 * (kBarKEmpty + 0));
       }
 #pragma unroll 1
       for (int j = 0; j < n_max && ok; ++j) {
         const int vs = j % kVStages;
         const int nxt = j + 1;
         const int ks = nxt % kKStages;
-        ok = wait_bar(bars + 8 * (kBarVFull + vs), (j / kVStages) & 1, abort_flag, 62);
+        ok = wait_bar_warp(bars + 8 * (kBarVFull + vs), (j / kVStages) & 1, abort_flag, 62);
         if (!ok) break;
         if (nxt < n_max) {
-          ok = wait_bar(bars + 8 * (kBarKFull + ks), (nxt / kKStages) & 1, abort_flag, 63);
+          ok = wait_bar_warp(bars + 8 * (kBarKFull + ks), (nxt / kKStages) & 1, abort_flag, 63);
           if (!ok) break;
         }
         if constexpr (!kInstBuf) {
           for (int t = 0; t < 2 && ok; ++t) {
             if (j < n_blk[t]) {
-              SAGE_TR(2, 10 + t, j);
-              ok = wait_bar(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
+              if (lane == 0) SAGE_TR(2, 10 + t, j);
+              ok = wait_bar_warp(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
               if (!ok) break;
               ptx::tc_fence_after();
-              SAGE_TR(2, 12 + t, j);
+              if (lane == 0) SAGE_TR(2, 12 + t, j);
               issue_pv(t, vs, j > 0);
-              ptx::tc_commit(bars + 8 * (kBarPvDone + t));
+              commit(bars + 8 * (kBarPvDone + t));
               if (nxt < n_blk[t]) {
                 issue_qk(t, ks);
-                ptx::tc_commit(bars + 8 * (kBarSFull + t));
+                commit(bars + 8 * (kBarSFull + t));
               }
-              SAGE_TR(2, 14 + t, j);
+              if (lane == 0) SAGE_TR(2, 14 + t, j);
             }
           }
         } else {
@@ -557,31 +572,31 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int ch = 0; ch < kChunks && ok; ++ch) {
             for (int t = 0; t < 2 && ok; ++t) {
               if (j < n_blk[t]) {
-                if (ch == 0) ok = wait_bar(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
-                else ok = wait_bar(bars + 8 * (kBarSFree + t), (j * kChunks + ch - 1) & 1, abort_flag, 66 + t);
+                if (ch == 0) ok = wait_bar_warp(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
+                else ok = wait_bar_warp(bars + 8 * (kBarSFree + t), (j * kChunks + ch - 1) & 1, abort_flag, 66 + t);
                 if (!ok) break;
                 ptx::tc_fence_after();
                 issue_pv_chunk(t, vs, ch);
-                ptx::tc_commit(bars + 8 * (kBarPvDone + t));
+                commit(bars + 8 * (kBarPvDone + t));
               }
             }
           }
           for (int t = 0; t < 2 && ok; ++t) {
             if (nxt < n_blk[t]) {
-              ok = wait_bar(bars + 8 * (kBarSFree + t), (j * kChunks + kChunks - 1) & 1, abort_flag, 68 + t);
+              ok = wait_bar_warp(bars + 8 * (kBarSFree + t), (j * kChunks + kChunks - 1) & 1, abort_flag, 68 + t);
               if (!ok) break;
               ptx::tc_fence_after();
               issue_qk(t, ks);
-              ptx::tc_commit(bars + 8 * (kBarSFull + t));
+              commit(bars + 8 * (kBarSFull + t));
             }
           }
         }
         if (!ok) break;
-        ptx::tc_commit(bars + 8 * (kBarVEmpty + vs));
-        if (nxt < n_max) ptx::tc_commit(bars + 8 * (kBarKEmpty + ks));
+        commit(bars + 8 * (kBarVEmpty + vs));
+        if (nxt < n_max) commit(bars + 8 * (kBarKEmpty + ks));
       }
       // everything this thread issued must have retired before tensor memory is released
-      ptx::tc_commit(bars + 8 * kBarDrain);
+      commit(bars + 8 * kBarDrain);
       for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(bars + 8 * kBarDrain, 0); ++i) {}
     }
   }

@@ -46,7 +46,8 @@ enum BarIdx {
   kBarPFull = kBarSFull + 4,              // [tile][buffer] = 4
   kBarPvDone = kBarPFull + 4,             // [tile] = 2, one phase per step
   kBarOFinal = kBarPvDone + 2,            // [tile] = 2, completes once: the tile's last P.V has retired
-  kBarDrain = kBarOFinal + 2,
+  kBarTurn = kBarOFinal + 2,              // [tile][warp] = 8: whose turn it is on the special-function unit
+  kBarDrain = kBarTurn + 8,
   kNumBars = kBarDrain + 1
 };
 
@@ -69,11 +70,39 @@ __host__ __device__ constexpr uint32_t idesc_qk64() {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((kStepKV >> 3) << 17) | ((kTileQ >> 4) << 24);
 }
 
+// Bounded wait for this warp's turn on the special-function unit; a finished peer never blocks us.
+__device__ __forceinline__ bool wait_turn(uint32_t bar, uint32_t parity, volatile unsigned char* peer_done,
+                                          volatile int* abort_flag, int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i)
+      if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (*peer_done != 0) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      atomicCAS(const_cast<int*>(abort_flag), 0, code);
+      return false;
+    }
+  }
+}
+
 // One softmax warpgroup: thread `row` (0..127) of tile `tile`; n_steps 64-key steps.
+//
+// The exponentials are the scarcest resource (16 per clock per SM, four per scheduler), and each
+// scheduler hosts one warp of either tile.  The two warps take turns on it: a warp evaluates its 64
+// exponentials while its peer stores P, fetches its next scores and finds their maximum, then hands
+// over.  Without the hand-over both warps reach their exponentials together and the unit idles while
+// both do the rest.
 template <int D, int PV_MODE, int OUT_DTYPE>
 __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars, uint32_t tmem_base,
-                                             volatile int* abort_flag, int tile, int row, int n_steps,
-                                             int q_row0, int b, int h, int h_kv) {
+                                             volatile int* abort_flag, volatile unsigned char* done_flags,
+                                             int tile, int row, int n_steps, int q_row0, int b, int h, int h_kv) {
+  const int wq = row >> 5;
+  const uint32_t bar_my_turn = bars + 8 * (kBarTurn + tile * 4 + wq);
+  const uint32_t bar_peer_turn = bars + 8 * (kBarTurn + (tile ^ 1) * 4 + wq);
+  volatile unsigned char* peer_done = done_flags + (tile ^ 1) * 4 + wq;
   constexpr bool kF16Acc = (PV_MODE == SAGE_B200_PV_F16);
   const uint32_t lane_base = static_cast<uint32_t>(row & ~31) << 16;
   const uint32_t t_tile = tmem_base + lane_base + tile * 256;
@@ -90,16 +119,29 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
   const float* ks_base = p.k_scale + (static_cast<int64_t>(b) * p.heads_kv + h_kv) * p.k_groups;
   const bool per_thread = (p.gran == SAGE_B200_GRAN_PER_THREAD);
   // k_scales of one step: four entries (per-thread grouping) or one (per-block); fetched one step ahead
+  // (volatile, so that the load stays where it is written - a full step ahead of its use)
   auto load_scales = [&](int step) -> float4 {
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
     if (per_thread) {
-      if (step * 4 + 3 < p.k_groups) return __ldg(reinterpret_cast<const float4*>(ks_base) + step);
-      return make_float4(0.f, 0.f, 0.f, 0.f);
+      if (step * 4 + 3 < p.k_groups)
+        asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+                     : "l"(ks_base + 4 * step));
+    } else if (step < p.k_groups) {
+      asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(r.x) : "l"(ks_base + step));
+      r.y = r.z = r.w = r.x;
     }
-    const float v = (step < p.k_groups) ? __ldg(ks_base + step) : 0.0f;
-    return make_float4(v, v, v, v);
+    return r;
   };
   float4 ks_next = load_scales(0);
 
+#ifdef SAGE_TRACE
+  long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tprev = clock64();
+#define SAGE_PH(k) do { const long long tn_ = clock64(); tacc[k] += tn_ - tprev; tprev = tn_; } while (0)
+#else
+#define SAGE_PH(k) do {} while (0)
+#endif
   float m_run = -INFINITY;     // true running maximum (base 2, scaled)
   float m_used = -INFINITY;    // reference point P and O are expressed against
   float d_sum = 0.0f;
@@ -110,6 +152,7 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     const int buf = i & 1;
     const int k0 = i * kStepKV;
     const uint32_t t_s = t_tile + buf * kStepKV;
+    SAGE_PH(7);
     const float4 ks = ks_next;
     if (i + 1 < n_steps) ks_next = load_scales(i + 1);
     float a[4];
@@ -117,18 +160,17 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     a[1] = p.scale_log2 * (q_sc * ks.y);
     a[2] = p.scale_log2 * (q_sc * ks.z);
     a[3] = p.scale_log2 * (q_sc * ks.w);
-
-    if (row == 0) SAGE_TR(tile, 1, i);
+    SAGE_PH(0);
     ok = wait_bar_warp(bars + 8 * (kBarSFull + tile * 2 + buf), (i >> 1) & 1, abort_flag, 10 + tile);
     if (!ok) break;
     ptx::tc_fence_after();
-    if (row == 0) SAGE_TR(tile, 2, i);
+    SAGE_PH(1);
 
     uint32_t s[64];
     ptx::tmem_ld32<0>(t_s + 0, s);
     ptx::tmem_ld32<32>(t_s + 32, s);
     ptx::tmem_wait_ld();
-    if (row == 0) SAGE_TR(tile, 3, i);
+    SAGE_PH(2);
 
     const bool need_mask = (k0 + kStepKV > p.len_kv) || (p.causal && (k0 + kStepKV - 1 > q_row0));
     float m_blk = -INFINITY;
@@ -181,7 +223,6 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     }
     // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
     const float m_ref = (m_used == -INFINITY) ? 0.0f : m_used;
-    if (row == 0) SAGE_TR(tile, 4, i);
 
     if (i > 0 && __any_sync(0xffffffffu, rescale)) {
       // O holds the sum through step i-1: its P.V must have retired before O is touched
@@ -215,6 +256,15 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       }
       ptx::tmem_wait_st();
     }
+
+    SAGE_PH(3);
+#ifdef SAGE_TURNS
+    // tile 0 goes first: its k-th turn follows the peer's (k-1)-th hand-over, tile 1's k-th follows
+    // tile 0's k-th
+    ok = __all_sync(0xffffffffu, wait_turn(bar_my_turn, tile == 0 ? ((i & 1) ^ 1) : (i & 1), peer_done, abort_flag, 70 + tile));
+    if (!ok) break;
+#endif
+    SAGE_PH(4);
 
     // P = 2^(S*a - m), packed to fp16 pairs in place
     float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
@@ -256,15 +306,26 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       }
     }
     d_sum = d_sum * alpha + ((sum0 + sum1) + (sum2 + sum3));
-    if (row == 0) SAGE_TR(tile, 5, i);
+    SAGE_PH(5);
+#ifdef SAGE_TURNS
+    __syncwarp();
+    if ((row & 31) == 0) ptx::mbar_arrive(bar_peer_turn);
+#endif
 
     ptx::tmem_st32<0>(t_s, s);
     ptx::tmem_wait_st();
     ptx::tc_fence_before();
     ptx::mbar_arrive(bars + 8 * (kBarPFull + tile * 2 + buf));
-    if (row == 0) SAGE_TR(tile, 6, i);
+    SAGE_PH(6);
   }
+#ifdef SAGE_TRACE
+  if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (row & 31) == 0) {
+    for (int k = 0; k < 8; ++k) p.trace[(tile * 4 + wq) * 8 + k] = tacc[k];
+  }
+#endif
 
+  __syncwarp();
+  if ((row & 31) == 0) done_flags[tile * 4 + wq] = 1;
   if (ok && n_steps > 0) {
     // A parity wait is only meaningful within one phase of the barrier's current phase; the per-step
     // barrier may be two phases behind here, so the end of the tile has a barrier of its own.
@@ -359,8 +420,11 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     ptx::mbar_init(bars + 8 * (kBarPvDone + 1), 1);
     ptx::mbar_init(bars + 8 * (kBarOFinal + 0), 1);
     ptx::mbar_init(bars + 8 * (kBarOFinal + 1), 1);
+    for (int t = 0; t < 8; ++t) ptx::mbar_init(bars + 8 * (kBarTurn + t), 1);
     ptx::mbar_init(bars + 8 * kBarDrain, 1);
     *abort_flag = 0;
+    abort_flag[1] = 0;   // per-tile "finished" flags, one byte per (tile, warp)
+    abort_flag[2] = 0;
     ptx::fence_barrier_init();
   }
   if (warp == 8) {
@@ -373,12 +437,13 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 8) {
-    ptx::reg_inc<208>();
+    ptx::reg_inc<224>();
     const int tile = warp >> 2;
-    softmax_role<D, PV_MODE, OUT_DTYPE>(p, bars, tmem_base, abort_flag, tile, threadIdx.x & 127, n_steps[tile],
-                                        q0 + tile * kTileQ, b, h, h_kv);
+    softmax_role<D, PV_MODE, OUT_DTYPE>(p, bars, tmem_base, abort_flag,
+                                        reinterpret_cast<volatile unsigned char*>(smem_gen + Plan::kMiscOff + 8), tile,
+                                        threadIdx.x & 127, n_steps[tile], q0 + tile * kTileQ, b, h, h_kv);
   } else {
-    ptx::reg_dec<88>();
+    ptx::reg_dec<56>();
     if (warp == 8 && lane == 0) {
       // ---------------- TMA producer ----------------
       ptx::prefetch_tensormap(&tm_q);
@@ -411,8 +476,10 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 0) &&
                           !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 1); ++i) {}
       }
-    } else if (warp == 9 && lane == 0) {
+    } else if (warp == 9) {
       // ---------------- MMA issuer ----------------
+      // The whole warp runs this loop and one elected lane issues: operands that are computed in
+      // converged code stay in uniform registers, which tcgen05.mma and tcgen05.commit read directly.
       constexpr int kRowBytesQK = (D == 64) ? 64 : 128;
       constexpr int kStepsQK = kRowBytesQK / 32;              // int8: 32 bytes of K per instruction
       const uint32_t idq = idesc_qk64();
@@ -424,40 +491,59 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint64_t v_desc0 = desc_mnmajor(smem_base + Plan::kVOff, kStageKV * 128);
 
       // S[t][step & 1] = Q_t . K(step)^T, 64 keys
-      auto issue_qk = [&](int t, int step) {
+      auto issue_qk = [&](int t, int step, uint32_t commit_bar) {
         const int stage = (step >> 1) % kKStages;
         const uint32_t d_t = tmem_base + t * 256 + (step & 1) * kStepKV;
         const uint64_t da0 = q_desc0 + static_cast<uint64_t>((t * Plan::kQBytes) >> 4);
         const uint64_t db0 = k_desc0 + static_cast<uint64_t>((stage * Plan::kKBytes + (step & 1) * kStepKV * kRowBytesQK) >> 4);
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int s = 0; s < kStepsQK; ++s)
-          ptx::mma_i8_ss(d_t, da0 + static_cast<uint64_t>(s * 2), db0 + static_cast<uint64_t>(s * 2), idq, s != 0);
+          for (int s = 0; s < kStepsQK; ++s)
+            ptx::mma_i8_ss(d_t, da0 + static_cast<uint64_t>(s * 2), db0 + static_cast<uint64_t>(s * 2), idq, s != 0);
+          ptx::tc_commit(commit_bar);
+        }
+        __syncwarp();
       };
       // O_t (+)= P(step) . V(step): 16 keys per instruction = 8 packed columns of P, 2 KB of every V panel
-      auto issue_pv = [&](int t, int step) {
+      auto issue_pv = [&](int t, int step, uint32_t commit_bar, bool last) {
         const int stage = (step >> 1) % kVStages;
         const uint32_t d_t = tmem_base + t * 256 + 128;
         const uint32_t a_t = tmem_base + t * 256 + (step & 1) * kStepKV;
         const uint64_t db0 = v_desc0 + static_cast<uint64_t>((stage * Plan::kVBytes + (step & 1) * kStepKV * 128) >> 4);
+        if (ptx::elect_one()) {
 #pragma unroll
-        for (int s = 0; s < kStepKV / 16; ++s)
-          ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>(s * 128), idp, (step > 0 || s != 0) ? 1u : 0u);
+          for (int s = 0; s < kStepKV / 16; ++s)
+            ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>(s * 128), idp, (step > 0 || s != 0) ? 1u : 0u);
+          ptx::tc_commit(commit_bar);
+          if (last) ptx::tc_commit(bars + 8 * (kBarOFinal + t));
+        }
+        __syncwarp();
+      };
+      auto commit_only = [&](uint32_t bar) {
+        if (ptx::elect_one()) ptx::tc_commit(bar);
+        __syncwarp();
       };
 
-      bool ok = wait_bar(bars + 8 * kBarQFull, 0, abort_flag, 60);
-      if (ok && n_max > 0) ok = wait_bar(bars + 8 * (kBarKFull + 0), 0, abort_flag, 61);
+      bool ok = wait_bar_warp(bars + 8 * kBarQFull, 0, abort_flag, 60);
+      if (ok && n_max > 0) ok = wait_bar_warp(bars + 8 * (kBarKFull + 0), 0, abort_flag, 61);
       if (ok && n_max > 0) {
         ptx::tc_fence_after();
         for (int st = 0; st < 2; ++st) {
           for (int t = 0; t < 2; ++t) {
             if (st < n_steps[t]) {
-              issue_qk(t, st);
-              ptx::tc_commit(bars + 8 * (kBarSFull + t * 2 + st));
+              issue_qk(t, st, bars + 8 * (kBarSFull + t * 2 + st));
             }
           }
         }
-        ptx::tc_commit(bars + 8 * (kBarKEmpty + 0));
+        commit_only(bars + 8 * (kBarKEmpty + 0));
       }
+#ifdef SAGE_TRACE
+      long long macc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      long long mprev = clock64();
+#define MMA_PH(k) do { const long long tn_ = clock64(); macc[k] += tn_ - mprev; mprev = tn_; } while (0)
+#else
+#define MMA_PH(k) do {} while (0)
+#endif
 #pragma unroll 1
       for (int i = 0; i < n_max && ok; ++i) {
         const int blk = i >> 1;
@@ -465,36 +551,40 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int nxt = i + 2;                       // the step whose Q.K^T reuses this S buffer
         const int ks = (nxt >> 1) % kKStages;
         if ((i & 1) == 0) {
-          ok = wait_bar(bars + 8 * (kBarVFull + vs), (blk / kVStages) & 1, abort_flag, 62);
+          ok = wait_bar_warp(bars + 8 * (kBarVFull + vs), (blk / kVStages) & 1, abort_flag, 62);
           if (!ok) break;
           if (nxt < n_max) {
-            ok = wait_bar(bars + 8 * (kBarKFull + ks), ((nxt >> 1) / kKStages) & 1, abort_flag, 63);
+            ok = wait_bar_warp(bars + 8 * (kBarKFull + ks), ((nxt >> 1) / kKStages) & 1, abort_flag, 63);
             if (!ok) break;
           }
         }
         for (int t = 0; t < 2 && ok; ++t) {
           if (i < n_steps[t]) {
-            SAGE_TR(2, 10 + t, i);
-            ok = wait_bar(bars + 8 * (kBarPFull + t * 2 + (i & 1)), (i >> 1) & 1, abort_flag, 64 + t);
+            MMA_PH(0);
+            ok = wait_bar_warp(bars + 8 * (kBarPFull + t * 2 + (i & 1)), (i >> 1) & 1, abort_flag, 64 + t);
             if (!ok) break;
             ptx::tc_fence_after();
-            SAGE_TR(2, 12 + t, i);
-            issue_pv(t, i);
-            ptx::tc_commit(bars + 8 * (kBarPvDone + t));
-            if (i == n_steps[t] - 1) ptx::tc_commit(bars + 8 * (kBarOFinal + t));
+            MMA_PH(1 + 3 * t);
+            issue_pv(t, i, bars + 8 * (kBarPvDone + t), i == n_steps[t] - 1);
+            MMA_PH(2 + 3 * t);
             if (nxt < n_steps[t]) {
-              issue_qk(t, nxt);
-              ptx::tc_commit(bars + 8 * (kBarSFull + t * 2 + (i & 1)));
+              issue_qk(t, nxt, bars + 8 * (kBarSFull + t * 2 + (i & 1)));
             }
-            SAGE_TR(2, 14 + t, i);
+            MMA_PH(3 + 3 * t);
           }
         }
         if (!ok) break;
-        if ((i & 1) == 1 || i == n_max - 1) ptx::tc_commit(bars + 8 * (kBarVEmpty + vs));
-        if ((i & 1) == 1 && nxt < n_max) ptx::tc_commit(bars + 8 * (kBarKEmpty + ks));
+        MMA_PH(0);
+        if ((i & 1) == 1 || i == n_max - 1) commit_only(bars + 8 * (kBarVEmpty + vs));
+        if ((i & 1) == 1 && nxt < n_max) commit_only(bars + 8 * (kBarKEmpty + ks));
+        MMA_PH(7);
       }
+#ifdef SAGE_TRACE
+      if (p.trace != nullptr && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+        for (int k = 0; k < 8; ++k) p.trace[64 + k] = macc[k];
+#endif
       // everything this thread issued must have retired before tensor memory is released
-      ptx::tc_commit(bars + 8 * kBarDrain);
+      commit_only(bars + 8 * kBarDrain);
       for (int i = 0; i < (1 << 20) && !ptx::mbar_try_wait(bars + 8 * kBarDrain, 0); ++i) {}
     }
   }
