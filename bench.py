@@ -285,7 +285,7 @@ def main():
     els_q = w["B"] * heads_local * w["N"] * w["D"]
     els_k = w["B"] * (kv_hi - kv_lo) * w["N"] * w["D"]
     qbytes = 3.0 * (els_q + els_k)
-    front_ms = kern_ms.get("mean_k", 0.0) + kern_ms.get("quant_qk", 0.0)
+    front_ms = kern_ms.get("quant_q", 0.0) + kern_ms.get("smooth_quant_k", 0.0)
     roofline["quant"] = {"bound": "hbm", "achieved": qbytes / (front_ms * 1e-3) / 1e9 if front_ms else None,
                          "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": (qbytes / (front_ms * 1e-3) / 1e9) / pk["hbm_gbs"] if front_ms else None}

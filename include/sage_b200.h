@@ -95,6 +95,23 @@ int sage_b200_quant_int8(const void* x, const void* mean, int8_t* out, float* sc
                          int blk, int warp, int group_kind, int div_mode, void* stream);
 
 /*
+ * K smoothing and quantisation in one call: channel mean of K (as sage_b200_mean_k) followed by the
+ * int8 quantisation of K - mean (as sage_b200_quant_int8 with the K per-thread or per-block
+ * grouping).  Replaces `km = k.mean(...)` plus the K half of per_thread_int8 / per_block_int8
+ * (sageattention/cuda_attn.py:167-187, sageattention/triton/quant_per_thread.py:182-203).
+ * K is processed in slices of whole batches (or of heads when batch == 1) of about `slice_bytes`
+ * bytes, mean then quantise per slice, so that the second read of a slice hits the L2 cache and K
+ * crosses HBM once; 64 MiB suits the 126 MB L2 of B200.  Results do not depend on the slicing.
+ *   km      out, (batch, heads, head_dim) contiguous, K's dtype
+ *   scratch at least sage_b200_smooth_quant_k_scratch_bytes(...) bytes
+ */
+size_t sage_b200_smooth_quant_k_scratch_bytes(int batch, int heads, int len, int head_dim, size_t slice_bytes);
+int sage_b200_smooth_quant_k(const void* k, void* km, int8_t* out, float* scale, void* scratch,
+                             size_t scratch_bytes, int dtype, int batch, int heads, int len, int head_dim,
+                             const int64_t k_strides[3], const int64_t out_strides[3], int blk, int warp,
+                             int group_kind, int div_mode, size_t slice_bytes, void* stream);
+
+/*
  * V cast to fp16.  Replaces `v.to(torch.float16)` (sageattention/cuda_attn.py:195,233,250).
  */
 int sage_b200_cast_v_f16(const void* v, void* out, int dtype, int batch, int heads, int len,

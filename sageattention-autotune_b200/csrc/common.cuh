@@ -46,8 +46,14 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&x)[8]) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    x[2 * i + 0] = to_f32<DTYPE>(static_cast<unsigned short>(w[i] & 0xffffu));
-    x[2 * i + 1] = to_f32<DTYPE>(static_cast<unsigned short>(w[i] >> 16));
+    if constexpr (DTYPE == SAGE_B200_BF16) {
+      x[2 * i + 0] = __uint_as_float(w[i] << 16);
+      x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      x[2 * i + 0] = f.x;
+      x[2 * i + 1] = f.y;
+    }
   }
 }
 

@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _capi as C
+from . import quant as Q
 from .quant import cast_v_fp16, mean_k, per_block_int8, per_thread_int8
 from .tile_table import SUPPORTED_QK_CONFIGS, select_qk_config
 
@@ -154,14 +155,20 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         return t if (t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
     q, k, v = _aligned(q), _aligned(k), _aligned(v)
 
-    with _Timed("mean_k"):
-        km = mean_k(k, tensor_layout) if smooth_k else None
     blk_q, blk_k, warp_q, warp_k = qk_config
-    with _Timed("quant_qk"):
-        if qk_quant_gran == "per_thread":
-            q_int8, q_scale, k_int8, k_scale = per_thread_int8(q, k, km, blk_q, warp_q, blk_k, warp_k, tensor_layout)
+    per_thread = qk_quant_gran == "per_thread"
+    with _Timed("quant_q"):
+        q_int8, q_scale = Q._quant_one(q, None, blk_q, warp_q if per_thread else blk_q,
+                                       C.GROUP_Q_THREAD if per_thread else C.GROUP_BLOCK, tensor_layout,
+                                       Q.default_div_mode())
+    with _Timed("smooth_quant_k"):
+        k_kind = C.GROUP_K_THREAD if per_thread else C.GROUP_BLOCK
+        k_warp = warp_k if per_thread else blk_k
+        if smooth_k:
+            km, k_int8, k_scale = Q.smooth_quant_k(k, blk_k, k_warp, k_kind, tensor_layout)
         else:
-            q_int8, q_scale, k_int8, k_scale = per_block_int8(q, k, km, blk_q, blk_k, tensor_layout)
+            km = None
+            k_int8, k_scale = Q._quant_one(k, None, blk_k, k_warp, k_kind, tensor_layout, Q.default_div_mode())
     with _Timed("cast_v"):
         v_fp16 = cast_v_fp16(v, tensor_layout)
 

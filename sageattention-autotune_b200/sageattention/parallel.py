@@ -40,11 +40,11 @@ def slice_heads(t: torch.Tensor, tensor_layout: str, lo: int, hi: int) -> torch.
 
 def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout: str = "HND",
                      group: Optional[dist.ProcessGroup] = None, gather: bool = True,
-                     attn_fn: Optional[Callable] = None, **kwargs):
+                     attn_fn: Optional[Callable] = None, num_kv_heads: Optional[int] = None, **kwargs):
     """Run attention on this rank's heads; optionally all-gather the full output.
 
     q_local/k_local/v_local hold only this rank's heads (as produced by `local_heads` +
-    `slice_heads`).  With gather=True every rank returns the output for all `num_q_heads` heads,
+    `slice_heads`); `num_kv_heads` is the global kv-head count (defaults to num_q_heads).  With gather=True every rank returns the output for all `num_q_heads` heads,
     in the input layout; with gather=False the local result is returned untouched and no
     collective is issued.  `attn_fn` defaults to sageattention.sageattn."""
     if attn_fn is None:
@@ -56,7 +56,8 @@ def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout:
     want_lse = isinstance(res, tuple)
     out, lse = res if want_lse else (res, None)
     h_dim = 1 if tensor_layout == "HND" else 2
-    per = -(-num_q_heads // world)
+    num_kv_heads = num_q_heads if num_kv_heads is None else num_kv_heads
+    per = -(-num_kv_heads // world) * (num_q_heads // num_kv_heads)     # q-heads per rank slot
 
     def gather_heads(x, dim):
         # equal-sized slots of `per` heads, head dim moved to the front so that each rank's

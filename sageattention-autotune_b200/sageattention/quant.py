@@ -30,45 +30,82 @@ def _check_in(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be 4-D with a contiguous last dimension.")
 
 
+def _mean_k_into(k, km, tensor_layout, scratch=None):
+    b, h, n, d = C.bhnd(k, tensor_layout)
+    L = C.lib()
+    nbytes = L.sage_b200_mean_k_scratch_bytes(b, h, n, d)
+    if scratch is None or scratch.numel() * 4 < nbytes:
+        scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=k.device)
+    with torch.cuda.device(k.device):
+        C.check(L.sage_b200_mean_k(k.data_ptr(), km.data_ptr(), scratch.data_ptr(), scratch.numel() * 4,
+                                   C.dtype_code(k.dtype), b, h, n, d, C.bhn_strides(k, tensor_layout),
+                                   C.stream_ptr(k.device)))
+    return scratch
+
+
 def mean_k(k: torch.Tensor, tensor_layout: str = "HND") -> torch.Tensor:
     """k.mean over the sequence, keepdim, in k's dtype (reference: cuda_attn.py:167-170)."""
     _check_in(k, "k")
     b, h, n, d = C.bhnd(k, tensor_layout)
     shape = (b, h, 1, d) if tensor_layout == "HND" else (b, 1, h, d)
     km = torch.empty(shape, dtype=k.dtype, device=k.device)
-    L = C.lib()
-    nbytes = L.sage_b200_mean_k_scratch_bytes(b, h, n, d)
-    scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=k.device)
-    with torch.cuda.device(k.device):
-        C.check(L.sage_b200_mean_k(k.data_ptr(), km.data_ptr(), scratch.data_ptr(), scratch.numel() * 4,
-                                   C.dtype_code(k.dtype), b, h, n, d, C.bhn_strides(k, tensor_layout),
-                                   C.stream_ptr(k.device)))
+    _mean_k_into(k, km, tensor_layout)
     return km
+
+
+def _groups(n, blk, warp, kind):
+    blocks = -(-n // blk)
+    if kind == C.GROUP_Q_THREAD:
+        return blocks * (blk // warp) * 8
+    if kind == C.GROUP_K_THREAD:
+        return blocks * (blk // warp) * 4
+    return blocks
+
+
+def _quant_into(x, mean, out, scale, blk, warp, kind, tensor_layout, div):
+    b, h, n, d = C.bhnd(x, tensor_layout)
+    with torch.cuda.device(x.device):
+        C.check(C.lib().sage_b200_quant_int8(
+            x.data_ptr(), 0 if mean is None else mean.data_ptr(), out.data_ptr(), scale.data_ptr(),
+            C.dtype_code(x.dtype), b, h, n, d, C.bhn_strides(x, tensor_layout), C.bhn_strides(out, tensor_layout),
+            blk, warp, kind, _DIV[div], C.stream_ptr(x.device)))
 
 
 def _quant_one(x, mean, blk, warp, kind, tensor_layout, div):
     b, h, n, d = C.bhnd(x, tensor_layout)
     out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
-    blocks = -(-n // blk)
-    if kind == C.GROUP_Q_THREAD:
-        groups = blocks * (blk // warp) * 8
-    elif kind == C.GROUP_K_THREAD:
-        groups = blocks * (blk // warp) * 4
-    else:
-        groups = blocks
-    scale = torch.empty((b, h, groups), dtype=torch.float32, device=x.device)
-    mean_ptr = 0
+    scale = torch.empty((b, h, _groups(n, blk, warp, kind)), dtype=torch.float32, device=x.device)
     if mean is not None:
         if mean.dtype != x.dtype or mean.numel() != b * h * d:
             raise ValueError("km must have k's dtype and one value per (batch, head, channel).")
         mean = mean.contiguous()
-        mean_ptr = mean.data_ptr()
-    with torch.cuda.device(x.device):
-        C.check(C.lib().sage_b200_quant_int8(
-            x.data_ptr(), mean_ptr, out.data_ptr(), scale.data_ptr(), C.dtype_code(x.dtype), b, h, n, d,
-            C.bhn_strides(x, tensor_layout), C.bhn_strides(out, tensor_layout), blk, warp, kind,
-            _DIV[div], C.stream_ptr(x.device)))
+    _quant_into(x, mean, out, scale, blk, warp, kind, tensor_layout, div)
     return out, scale
+
+
+# K is read twice (mean, then quantise).  Doing both for a slice of heads that fits in the 126 MB L2
+# before moving on makes the second read an L2 hit, so K crosses HBM once.
+_L2_SLICE_BYTES = 64 << 20
+
+
+def smooth_quant_k(k, blk, warp, kind, tensor_layout="HND", div=None):
+    """(km, k_int8, k_scale): channel mean of K and int8 quantisation of K - mean, processed in
+    L2-sized slices of whole batches (or of heads when batch == 1)."""
+    _check_in(k, "k")
+    div = div or default_div_mode()
+    b, h, n, d = C.bhnd(k, tensor_layout)
+    km = torch.empty((b, h, 1, d) if tensor_layout == "HND" else (b, 1, h, d), dtype=k.dtype, device=k.device)
+    k8 = torch.empty(k.shape, dtype=torch.int8, device=k.device)
+    ks = torch.empty((b, h, _groups(n, blk, warp, kind)), dtype=torch.float32, device=k.device)
+    L = C.lib()
+    nbytes = L.sage_b200_smooth_quant_k_scratch_bytes(b, h, n, d, _L2_SLICE_BYTES)
+    scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=k.device)
+    with torch.cuda.device(k.device):
+        C.check(L.sage_b200_smooth_quant_k(
+            k.data_ptr(), km.data_ptr(), k8.data_ptr(), ks.data_ptr(), scratch.data_ptr(), scratch.numel() * 4,
+            C.dtype_code(k.dtype), b, h, n, d, C.bhn_strides(k, tensor_layout), C.bhn_strides(k8, tensor_layout),
+            blk, warp, kind, _DIV[div], _L2_SLICE_BYTES, C.stream_ptr(k.device)))
+    return km, k8, ks
 
 
 def per_thread_int8(q, k, km=None, BLKQ=128, WARPQ=32, BLKK=64, WARPK=64, tensor_layout="HND", div=None):

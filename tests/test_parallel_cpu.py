@@ -51,7 +51,8 @@ def _worker(rank, world, port, layout, hq, hkv, q):
         qf, kf, vf = (torch.randn(shape(h), generator=g) for h in (hq, hkv, hkv))
         (ql, qh), (kl, kh) = local_heads(hq, hkv, world, rank)
         args = (slice_heads(qf, layout, ql, qh), slice_heads(kf, layout, kl, kh), slice_heads(vf, layout, kl, kh))
-        out, lse = sageattn_sharded(*args, num_q_heads=hq, tensor_layout=layout, attn_fn=_fake_attn, return_lse=True)
+        out, lse = sageattn_sharded(*args, num_q_heads=hq, num_kv_heads=hkv, tensor_layout=layout, attn_fn=_fake_attn,
+                                    return_lse=True)
         exp, exp_lse = _fake_attn(qf, kf, vf, layout, True)
         ok = torch.allclose(out, exp) and torch.allclose(lse, exp_lse) and out.shape == qf.shape
         loc = sageattn_sharded(*args, num_q_heads=hq, tensor_layout=layout, attn_fn=_fake_attn, gather=False)

@@ -140,3 +140,20 @@ def test_quant_idempotent_properties_at_full_size():
     amax = q.float().abs().view(B, H, N // 32, 4, 8, D).amax(dim=(3, 5)).cpu()
     assert torch.equal(qs.view(B, H, N // 32, 8).cpu(), amax / 127.0 + 1e-7)
     assert int(q8.abs().max()) == 127
+
+
+@pytest.mark.parametrize("B,H,layout", [(1, 6, "HND"), (1, 5, "NHD"), (3, 2, "HND"), (3, 2, "NHD")])
+def test_smooth_quant_k_slicing_does_not_change_results(B, H, layout, monkeypatch):
+    """K mean + quantisation processed in L2-sized slices (of heads, or of batches) gives exactly the
+    mean and the int8 values / scales of the unsliced two-step path."""
+    from sageattention import _capi as C
+    from sageattention import quant
+    cuda_or_fail()
+    _, k, _ = make_qkv(B, H, H, 700, 128, torch.bfloat16, layout, seed=B * 10 + H, k_bias=2.0)
+    km_ref = quant.mean_k(k, layout)
+    k8_ref, ks_ref = quant._quant_one(k, km_ref, 64, 64, C.GROUP_K_THREAD, layout, "full")
+    for slice_bytes in (1, 2 * 700 * 128 * 2, 64 << 20):
+        monkeypatch.setattr(quant, "_L2_SLICE_BYTES", slice_bytes)
+        km, k8, ks = quant.smooth_quant_k(k, 64, 64, C.GROUP_K_THREAD, layout, "full")
+        torch.cuda.synchronize()
+        assert torch.equal(km, km_ref) and torch.equal(k8, k8_ref) and torch.equal(ks, ks_ref), slice_bytes
