@@ -74,6 +74,24 @@ int sage_b200_mean_k(const void* k, void* km, void* scratch, size_t scratch_byte
                      void* stream);
 
 /*
+ * Channel mean of K for callers that must not allocate.  (No counterpart in the reference: it was
+ * added for hosts that cannot call cudaMalloc around this library - code running inside a CUDA
+ * graph capture or a stream-ordered region where allocation is forbidden, plugins handed a fixed
+ * memory budget, and real-time loops that may not touch the allocator.)
+ * Same result as sage_b200_mean_k, bit for bit; the partial sums of the two-stage reduction live in
+ * a buffer built into the library (sage_b200_mean_k_static_capacity_bytes() = 2 MiB, held by every GPU
+ * that loads the library until the process exits).  A shape whose partial sums do not fit is refused
+ * with SAGE_B200_ERR_INVALID; sage_b200_mean_k_scratch_bytes(...) tells how much a shape needs.
+ * The first call on each device looks up the buffer's device address (cudaGetSymbolAddress); make
+ * that first call outside any stream capture.  No cudaMalloc/cudaFree or allocating library routine
+ * is called.  All calls on a device share the one buffer: the kernels overwrite all of it that they
+ * read, nothing needs clearing, but two calls that overlap on the GPU (different streams) race.
+ */
+size_t sage_b200_mean_k_static_capacity_bytes(void);
+int sage_b200_mean_k_static(const void* k, void* km, int dtype, int batch, int heads, int len,
+                            int head_dim, const int64_t k_strides[3], void* stream);
+
+/*
  * int8 quantisation of Q or K with fp32 scales.
  * Replaces quant_query_per_thread_int8_kernel / quant_key_per_thread_int8_kernel
  * (sageattention/triton/quant_per_thread.py:22-115, host wrapper :118-205) and

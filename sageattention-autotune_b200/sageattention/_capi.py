@@ -21,6 +21,7 @@ PV_F32, PV_F16, PV_F16_F32 = 0, 1, 2
 
 EXPORTS = (
     "sage_b200_version", "sage_b200_last_error", "sage_b200_mean_k_scratch_bytes", "sage_b200_mean_k",
+    "sage_b200_mean_k_static_capacity_bytes", "sage_b200_mean_k_static",
     "sage_b200_quant_int8", "sage_b200_smooth_quant_k_scratch_bytes", "sage_b200_smooth_quant_k",
     "sage_b200_cast_v_f16", "sage_b200_attn_fwd",
 )
@@ -48,6 +49,9 @@ def lib() -> ctypes.CDLL:
         L.sage_b200_mean_k_scratch_bytes.argtypes = [i, i, i, i]
         L.sage_b200_mean_k.restype = i
         L.sage_b200_mean_k.argtypes = [vp, vp, vp, ctypes.c_size_t, i, i, i, i, i, i64p, vp]
+        L.sage_b200_mean_k_static_capacity_bytes.restype = ctypes.c_size_t
+        L.sage_b200_mean_k_static.restype = i
+        L.sage_b200_mean_k_static.argtypes = [vp, vp, i, i, i, i, i, i64p, vp]
         L.sage_b200_quant_int8.restype = i
         L.sage_b200_quant_int8.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i64p, i64p, i, i, i, i, vp]
         L.sage_b200_smooth_quant_k_scratch_bytes.restype = ctypes.c_size_t
