@@ -241,10 +241,38 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+__device__ __forceinline__ unsigned long long sub2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
   unsigned long long r;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
+}
+
+// 2^y for a pair of arguments y <= 0 without the special-function unit (whose instructions hold the
+// scheduler's dispatch port for most of their 8 cycles on this GPU): split y = n + f with n integer
+// and f in [-0.5, 0.5] by a round-to-nearest add of 1.5*2^23, evaluate a degree-3 polynomial for
+// 2^f (maximum relative error 7.5e-5, well under the 4.9e-4 rounding of the fp16 result), and add n
+// to the exponent field.  Arguments below -126 are clamped; their results are far below fp16 range.
+__device__ __forceinline__ void exp2_pair_poly(unsigned long long y2, float& p0, float& p1) {
+  const unsigned long long magic = pack2(12582912.0f, 12582912.0f);
+  const unsigned long long fr = add2(y2, magic);            // integer n in the low mantissa bits
+  const unsigned long long f = add2(y2, sub2(magic, fr));   // y - n, exact
+  unsigned long long q = fma2(pack2(0.055170975625514984f, 0.055170975625514984f), f,
+                              pack2(0.24260970950126648f, 0.24260970950126648f));
+  q = fma2(q, f, pack2(0.6932609677314758f, 0.6932609677314758f));
+  q = fma2(q, f, pack2(0.9999281764030457f, 0.9999281764030457f));
+  float q0, q1, r0, r1;
+  unpack2(q, q0, q1);
+  unpack2(fr, r0, r1);
+  // n is clamped at -126 on its bit pattern (positive floats order like integers)
+  const uint32_t n0 = max(__float_as_uint(r0), 0x4B400000u - 126u);
+  const uint32_t n1 = max(__float_as_uint(r1), 0x4B400000u - 126u);
+  p0 = __uint_as_float(__float_as_uint(q0) + (n0 << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (n1 << 23));
 }
 
 }  // namespace ptx
