@@ -41,6 +41,7 @@ WORKLOADS = {
     "c5_32k_fp32": dict(B=1, Hq=64, Hkv=64, N=32768, D=128, dtype="float16", causal=True, pv="fp32", layout="HND", seed=4),
     "c2_sd": dict(B=16, Hq=10, Hkv=10, N=4096, D=64, dtype="float16", causal=False, pv="fp16+fp32", layout="HND", seed=1, k_bias=3.0),
     "c3_gqa": dict(B=4, Hq=32, Hkv=8, N=8192, D=128, dtype="bfloat16", causal=True, pv="fp32", layout="NHD", seed=2, k_outliers=20.0),
+    "c4_dit_fp8": dict(B=1, Hq=24, Hkv=24, N=75600, D=128, dtype="bfloat16", causal=False, pv="fp8", layout="HND", seed=3, k_bias=2.0),
     "c4_dit": dict(B=1, Hq=24, Hkv=24, N=75600, D=128, dtype="bfloat16", causal=False, pv="fp32", layout="HND", seed=3, k_bias=2.0),
 }
 
@@ -224,6 +225,10 @@ def main():
     heads_local = q_hi - q_lo
     q, k, v = make_inputs(w, kv_lo, kv_hi, dev)
     kw = dict(tensor_layout=w["layout"], is_causal=w["causal"], pv_accum_dtype=w["pv"], smooth_k=True)
+    attn_call = sageattention.sageattn
+    if w["pv"] == "fp8":     # e4m3 P.V variant: its own entry point, fp32 accumulation
+        kw["pv_accum_dtype"] = "fp32"
+        attn_call = sageattention.sageattn_qk_int8_pv_fp8_cuda
 
     def barrier():
         if world > 1:
@@ -248,7 +253,7 @@ def main():
     out_holder = {}
 
     def step():
-        out_holder["o"] = sageattention.sageattn(q, k, v, **kw) if heads_local > 0 else None
+        out_holder["o"] = attn_call(q, k, v, **kw) if heads_local > 0 else None
 
     warmup = max(3, args.warmup)
     sampler = ClockSampler(local_rank)

@@ -56,6 +56,7 @@ extern "C" {
 #define SAGE_B200_PV_F32     0   /* "fp32"      */
 #define SAGE_B200_PV_F16     1   /* "fp16"      */
 #define SAGE_B200_PV_F16_F32 2   /* "fp16+fp32" */
+#define SAGE_B200_PV_F8      3   /* fp8 e4m3 P and V, fp32 accumulate (sage_b200_attn_fwd_fp8 only) */
 
 int sage_b200_version(void);
 const char* sage_b200_last_error(void);
@@ -157,6 +158,35 @@ int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* ou
                        const int64_t v_strides[3], const int64_t o_strides[3], int is_causal,
                        float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k,
                        int granularity, int pv_accum, void* stream);
+
+/*
+ * V in fp8 e4m3 with one fp32 scale per (batch, head, channel): scale = max|v| over the sequence / 448,
+ * v_fp8 = e4m3(v / scale), round to nearest, saturating.  The reference has no fp8 path in this
+ * tree (sageattention/core.py:18-21 exports sageattn_qk_int8_pv_fp8_cuda = None; the kernels live on
+ * an un-vendored branch), so this follows the published SageAttention2 scheme (per-channel V scale).
+ *   v        16-bit input by strides;  out: 1 byte per element by out_strides (head_dim contiguous)
+ *   v_scale  out, fp32 (batch, heads, head_dim) contiguous
+ *   scratch  at least sage_b200_quant_v_fp8_scratch_bytes(...) bytes (per-slice channel maxima)
+ */
+size_t sage_b200_quant_v_fp8_scratch_bytes(int batch, int heads, int len, int head_dim);
+int sage_b200_quant_v_fp8(const void* v, void* out, float* v_scale, void* scratch, size_t scratch_bytes,
+                          int dtype, int batch, int heads, int len, int head_dim, const int64_t v_strides[3],
+                          const int64_t out_strides[3], void* stream);
+
+/*
+ * Attention core with fp8 P.V: same as sage_b200_attn_fwd with pv_accum = SAGE_B200_PV_F8, plus
+ *   v        fp8 e4m3 by strides (as written by sage_b200_quant_v_fp8)
+ *   v_scale  fp32 (batch, heads_kv, head_dim) contiguous
+ * P is scaled by 448 before it is rounded to e4m3 (the factor cancels between O and the row sum),
+ * the accumulator is fp32.  No counterpart in this reference tree (see sage_b200_quant_v_fp8).
+ */
+int sage_b200_attn_fwd_fp8(const int8_t* q, const int8_t* k, const void* v, const float* v_scale, void* out,
+                           const float* q_scale, const float* k_scale, float* lse, int32_t* status,
+                           int out_dtype, int batch, int heads_q, int heads_kv, int len_q, int len_kv,
+                           int head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
+                           const int64_t v_strides[3], const int64_t o_strides[3], int is_causal,
+                           float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k, int granularity,
+                           void* stream);
 
 #ifdef __cplusplus
 }

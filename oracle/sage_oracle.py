@@ -179,7 +179,7 @@ def expand_k_scale(k_scale: torch.Tensor, nk: int, BLKK: int, WARPK: int, granul
 def attend(q_int8, k_int8, v16, q_scale, k_scale, tensor_layout="HND", is_causal=False,
            sm_scale=None, pv_accum_dtype="fp32", granularity="per_thread",
            BLKQ=128, WARPQ=32, BLKK=64, WARPK=64, out_dtype=torch.float16,
-           return_lse=False, p_dtype=torch.float16):
+           return_lse=False, p_dtype=torch.float16, p_gain=1.0, sum_rounded=True):
     """Flash-style forward on pre-quantised Q/K, in the reference's operation order:
     per BLKK-key block  S -> scale -> running max (base 2) -> P = 2^(S*a - m) -> P16 ->
     d += rowsum(P16) -> O = O*alpha + P16 @ V16, then O * (1/d).  ``pv_accum_dtype``:
@@ -228,8 +228,8 @@ def attend(q_int8, k_int8, v16, q_scale, k_scale, tensor_layout="HND", is_causal
             m_new = torch.maximum(m, s.max(dim=-1).values)
             alpha = torch.exp2(m - m_new)
             p = torch.exp2(s - m_new[..., None])
-            p16 = p.to(p_dtype).float()
-            d = d * alpha + p16.sum(dim=-1)
+            p16 = (p * p_gain).to(p_dtype).float() / p_gain
+            d = d * alpha + (p16 if sum_rounded else p).sum(dim=-1)
             pv = torch.matmul(p16, v[:, :, k0:k1])
             if pv_accum_dtype == "fp32":
                 acc = acc * alpha[..., None] + pv
@@ -247,6 +247,31 @@ def attend(q_int8, k_int8, v16, q_scale, k_scale, tensor_layout="HND", is_causal
     if return_lse:
         return out, lse
     return out
+
+
+def quant_v_fp8(v, tensor_layout="HND"):
+    """V in fp8 e4m3 with one scale per (batch, head, channel): scale = max(max|v|, 1e-8) * (1/448),
+    v_q = e4m3(v / scale).  No counterpart in the reference tree (its fp8 kernels live on an
+    un-vendored branch); this follows the published SageAttention2 scheme and is parity-unpinned."""
+    vb = to_bhnd(v, tensor_layout).float()
+    amax = vb.abs().amax(dim=2)                                        # (B,H,D)
+    scale = (torch.clamp(amax, min=1e-8).numpy().astype(np.float32) * np.float32(1.0 / 448.0)).astype(np.float32)
+    scale = torch.from_numpy(scale)
+    vq = (vb / scale[:, :, None, :]).to(torch.float8_e4m3fn)
+    return from_bhnd(vq, tensor_layout).contiguous(), scale
+
+
+def attend_fp8(q_int8, k_int8, v_fp8, v_scale, q_scale, k_scale, tensor_layout="HND", is_causal=False,
+               sm_scale=None, granularity="per_thread", BLKQ=128, WARPQ=32, BLKK=64, WARPK=64,
+               out_dtype=torch.float16, return_lse=False):
+    """attend() with e4m3 P.V: P is scaled by 448 and rounded to e4m3 before the product (the factor
+    cancels against the row sum, which adds the unrounded values), V carries its per-channel scale."""
+    v_deq = to_bhnd(v_fp8, tensor_layout).float() * v_scale[:, :, None, :]
+    # reuse attend(): 448 * P rounded to e4m3 == 448 * (P rounded to e4m3 with the exponent shifted)
+    res = attend(q_int8, k_int8, from_bhnd(v_deq, tensor_layout), q_scale, k_scale, tensor_layout, is_causal,
+                 sm_scale, "fp32", granularity, BLKQ, WARPQ, BLKK, WARPK, out_dtype, return_lse,
+                 p_dtype=torch.float8_e4m3fn, p_gain=448.0, sum_rounded=False)
+    return res
 
 
 def lse_correction(q, km, tensor_layout):

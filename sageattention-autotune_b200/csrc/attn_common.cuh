@@ -23,6 +23,7 @@ constexpr float kLazyRescale = 8.0f;              // fp32 accumulators: rescale 
 struct AttnParams {
   const float* q_scale;
   const float* k_scale;
+  const float* v_scale;          // fp8 P.V only: (batch, heads_kv, head_dim)
   void* out;
   float* lse;
   int32_t* status;
@@ -102,6 +103,21 @@ __host__ __device__ constexpr uint32_t idesc_pv() {
   return ((F16_ACC ? 0u : 1u) << 4) | (0u << 7) | (0u << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) |
          ((kTileQ >> 4) << 24);
 }
+
+// fp8 P.V: e4m3 x e4m3 -> fp32, A from tensor memory, B MN-major, M = 128, N = D
+template <int D>
+__host__ __device__ constexpr uint32_t idesc_pv_f8() {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (1u << 16) | ((uint32_t(D) >> 3) << 17) | ((kTileQ >> 4) << 24);
+}
+// MN-major fp8 operand: V as [keys][D bytes], D = 128 -> 128-byte swizzle, D = 64 -> 64-byte swizzle
+template <int D>
+__device__ __forceinline__ uint64_t desc_mnmajor_f8(uint32_t smem_addr) {
+  constexpr uint64_t layout = (D == 128) ? 2 : 4;
+  constexpr uint64_t sbo = (8 * D) >> 4;                     // 8 keys
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (sbo << 32) |
+         (uint64_t(1) << 46) | (layout << 61);
+}
+constexpr float kLog2Of448 = 8.807354922057604f;             // P is scaled by 448 before rounding to e4m3
 
 template <int OUT_DTYPE>
 __device__ __forceinline__ uint32_t pack_out(float lo, float hi) {

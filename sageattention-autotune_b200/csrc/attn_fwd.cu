@@ -65,9 +65,9 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   }();
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
   int smem;
-  if constexpr (PV_MODE == SAGE_B200_PV_F16_F32) {
+  if constexpr (PV_MODE == SAGE_B200_PV_F16_F32 || PV_MODE == SAGE_B200_PV_F8) {
     kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
-    smem = v1::SmemPlan<D>::kDynamic;
+    smem = v1::SmemPlan<D, PV_MODE == SAGE_B200_PV_F8>::kDynamic;
   } else {
     kern = force_v1 ? v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE> : v2::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
     smem = force_v1 ? v1::SmemPlan<D>::kDynamic : v2::SmemPlan<D>::kDynamic;
@@ -106,6 +106,7 @@ static int launch_attn_mode(int pv_accum, int out_dtype, const CUtensorMap& mq, 
   switch (pv_accum) {
     case SAGE_B200_PV_F32: return launch_attn_out<D, SAGE_B200_PV_F32>(out_dtype, mq, mk, mv, p, grid, stream);
     case SAGE_B200_PV_F16: return launch_attn_out<D, SAGE_B200_PV_F16>(out_dtype, mq, mk, mv, p, grid, stream);
+    case SAGE_B200_PV_F8: return launch_attn_out<D, SAGE_B200_PV_F8>(out_dtype, mq, mk, mv, p, grid, stream);
     default: return launch_attn_out<D, SAGE_B200_PV_F16_F32>(out_dtype, mq, mk, mv, p, grid, stream);
   }
 }
@@ -119,7 +120,7 @@ static long long* g_trace = nullptr;
 extern "C" void sage_b200_set_trace(long long* ptr) { g_trace = ptr; }
 #endif
 
-extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* out,
+static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const float* v_scale, void* out,
                                   const float* q_scale, const float* k_scale, float* lse, int32_t* status,
                                   int out_dtype, int batch, int heads_q, int heads_kv, int len_q, int len_kv,
                                   int head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
@@ -135,7 +136,10 @@ extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* 
   SAGE_REQUIRE(heads_q % heads_kv == 0, "attn_fwd: num_qo_heads (%d) must be divisible by num_kv_heads (%d)", heads_q, heads_kv);
   SAGE_REQUIRE(granularity == SAGE_B200_GRAN_PER_THREAD || granularity == SAGE_B200_GRAN_PER_BLOCK,
                "attn_fwd: unknown granularity %d", granularity);
-  SAGE_REQUIRE(pv_accum >= 0 && pv_accum <= 2, "attn_fwd: unknown pv_accum %d", pv_accum);
+  SAGE_REQUIRE(pv_accum >= 0 && pv_accum <= 3, "attn_fwd: unknown pv_accum %d", pv_accum);
+  SAGE_REQUIRE((pv_accum == SAGE_B200_PV_F8) == (v_scale != nullptr),
+               "attn_fwd: the fp8 mode (and only it) takes a v_scale; use sage_b200_attn_fwd_fp8");
+  SAGE_REQUIRE(v_scale == nullptr || aligned16(v_scale), "attn_fwd: v_scale must be 16-byte aligned");
   if (head_dim != 64 && head_dim != 128) {
     if (head_dim == 256)
       return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: head_dim 256 is not built yet");
@@ -155,6 +159,7 @@ extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* 
   AttnParams p;
   p.q_scale = q_scale;
   p.k_scale = k_scale;
+  p.v_scale = v_scale;
   p.out = out;
   p.lse = lse;
   p.status = status;
@@ -189,7 +194,10 @@ extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* 
   if (rc) return rc;
   rc = make_map(&mk, k, 1, batch, heads_kv, len_kv, head_dim, k_strides, head_dim, kStageRows, swz_qk, "k");
   if (rc) return rc;
-  rc = make_map(&mv, v, 2, batch, heads_kv, len_kv, head_dim, v_strides, 64, kStageRows, CU_TENSOR_MAP_SWIZZLE_128B, "v");
+  if (pv_accum == SAGE_B200_PV_F8)
+    rc = make_map(&mv, v, 1, batch, heads_kv, len_kv, head_dim, v_strides, head_dim, kStageRows, swz_qk, "v");
+  else
+    rc = make_map(&mv, v, 2, batch, heads_kv, len_kv, head_dim, v_strides, 64, kStageRows, CU_TENSOR_MAP_SWIZZLE_128B, "v");
   if (rc) return rc;
 
   const dim3 grid((len_q + 2 * kTileQ - 1) / (2 * kTileQ), heads_q, batch);
@@ -197,3 +205,30 @@ extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* 
   return launch_attn_mode<128>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
 }
 
+
+extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* out,
+                                  const float* q_scale, const float* k_scale, float* lse, int32_t* status,
+                                  int out_dtype, int batch, int heads_q, int heads_kv, int len_q, int len_kv,
+                                  int head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
+                                  const int64_t v_strides[3], const int64_t o_strides[3], int is_causal,
+                                  float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k,
+                                  int granularity, int pv_accum, void* stream) {
+  if (pv_accum == SAGE_B200_PV_F8)
+    return fail(SAGE_B200_ERR_INVALID, "attn_fwd: the fp8 mode needs a v_scale; use sage_b200_attn_fwd_fp8");
+  return attn_fwd_impl(q, k, v, nullptr, out, q_scale, k_scale, lse, status, out_dtype, batch, heads_q, heads_kv,
+                       len_q, len_kv, head_dim, q_strides, k_strides, v_strides, o_strides, is_causal, sm_scale,
+                       blk_q, blk_k, warp_q, warp_k, granularity, pv_accum, stream);
+}
+
+extern "C" int sage_b200_attn_fwd_fp8(const int8_t* q, const int8_t* k, const void* v, const float* v_scale,
+                                      void* out, const float* q_scale, const float* k_scale, float* lse,
+                                      int32_t* status, int out_dtype, int batch, int heads_q, int heads_kv,
+                                      int len_q, int len_kv, int head_dim, const int64_t q_strides[3],
+                                      const int64_t k_strides[3], const int64_t v_strides[3],
+                                      const int64_t o_strides[3], int is_causal, float sm_scale, int blk_q,
+                                      int blk_k, int warp_q, int warp_k, int granularity, void* stream) {
+  SAGE_REQUIRE(v_scale != nullptr, "attn_fwd_fp8: null v_scale");
+  return attn_fwd_impl(q, k, v, v_scale, out, q_scale, k_scale, lse, status, out_dtype, batch, heads_q, heads_kv,
+                       len_q, len_kv, head_dim, q_strides, k_strides, v_strides, o_strides, is_causal, sm_scale,
+                       blk_q, blk_k, warp_q, warp_k, granularity, SAGE_B200_PV_F8, stream);
+}

@@ -50,11 +50,11 @@ enum BarIdx {
   kNumBars = kBarDrain + 1
 };
 
-template <int D>
+template <int D, bool F8 = false>
 struct SmemPlan {
   static constexpr int kQBytes = kTileQ * D;                 // int8
   static constexpr int kKBytes = kBlockKV * D;               // int8
-  static constexpr int kVBytes = kBlockKV * D * 2;           // fp16
+  static constexpr int kVBytes = kBlockKV * D * (F8 ? 1 : 2);  // fp16, or e4m3
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + 2 * kQBytes;
   static constexpr int kVOff = kKOff + kKStages * kKBytes;
@@ -74,6 +74,7 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
                                              int q_row0, int b, int h, int h_kv) {
   constexpr bool kF16Acc = (PV_MODE == SAGE_B200_PV_F16);
   constexpr bool kInstBuf = (PV_MODE == SAGE_B200_PV_F16_F32);
+  constexpr bool kFp8 = (PV_MODE == SAGE_B200_PV_F8);
   const uint32_t lane_base = static_cast<uint32_t>(row & ~31) << 16;
   const uint32_t t_s = tmem_base + lane_base + tile * 256;
   const uint32_t t_p = t_s;
@@ -177,14 +178,15 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       m_used = m_run;
     } else {
       const float grow = m_run - m_used;
-      if ((kF16Acc || kInstBuf) ? (grow > 0.0f) : (grow > kLazyRescale)) {
+      // (fp8: P must stay <= 1 so that 448*P fits e4m3, hence no lazy rescale)
+      if ((kF16Acc || kInstBuf || kFp8) ? (grow > 0.0f) : (grow > kLazyRescale)) {
         alpha = ptx::ex2(m_used - m_run);
         m_used = m_run;
         rescale = true;
       }
     }
     // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
-    const float m_ref = (m_used == -INFINITY) ? 0.0f : m_used;
+    const float m_ref = ((m_used == -INFINITY) ? 0.0f : m_used) - (kFp8 ? kLog2Of448 : 0.0f);
 
     if constexpr (!kInstBuf) {
       if (j > 0 && __any_sync(0xffffffffu, rescale)) {
@@ -259,25 +261,36 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
         }
         acc0 = ptx::add2(acc0, ptx::pack2(p0, p1));
         acc1 = ptx::add2(acc1, ptx::pack2(p2, p3));
-        s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
-        s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
+        if constexpr (kFp8) {
+          s[c / 4] = ptx::pack_e4m3x4(p0, p1, p2, p3);
+        } else {
+          s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
+          s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
+        }
       }
       ptx::unpack2(acc0, sum0, sum1);
       ptx::unpack2(acc1, sum2, sum3);
     } else {
 #pragma unroll
-      for (int c = 0; c < 128; c += 2) {
+      for (int c = 0; c < 128; c += 4) {
         const float p0 = ptx::ex2(__uint_as_float(s[c + 0]) - m_ref);
         const float p1 = ptx::ex2(__uint_as_float(s[c + 1]) - m_ref);
-        sum0 += p0; sum1 += p1;
-        s[c / 2] = ptx::pack_f16x2(p0, p1);
+        const float p2 = ptx::ex2(__uint_as_float(s[c + 2]) - m_ref);
+        const float p3 = ptx::ex2(__uint_as_float(s[c + 3]) - m_ref);
+        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+        if constexpr (kFp8) {
+          s[c / 4] = ptx::pack_e4m3x4(p0, p1, p2, p3);
+        } else {
+          s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
+          s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
+        }
       }
     }
     d_sum = d_sum * alpha + ((sum0 + sum1) + (sum2 + sum3));
 
     if (row == 0) SAGE_TR(tile, 5, j);
     ptx::tmem_st32<0>(t_p + 0, s);
-    ptx::tmem_st32<32>(t_p + 32, s);
+    if constexpr (!kFp8) ptx::tmem_st32<32>(t_p + 32, s);     // e4m3: four keys per column, 32 columns
     ptx::tmem_wait_st();
     ptx::tc_fence_before();
     ptx::mbar_arrive(bar_p_full);
@@ -353,9 +366,20 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
         ptx::tmem_ld32<0>(t_o + c0, o);
         ptx::tmem_wait_ld();
         uint32_t w[16];
+        if constexpr (kFp8) {
+          const float4* vs = reinterpret_cast<const float4*>(
+              p.v_scale + (static_cast<int64_t>(b) * p.heads_kv + h_kv) * D + c0);
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          w[i] = pack_out<OUT_DTYPE>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+          for (int i = 0; i < 8; ++i) {
+            const float4 sc = __ldg(vs + i);
+            w[2 * i] = pack_out<OUT_DTYPE>(__uint_as_float(o[4 * i]) * inv * sc.x, __uint_as_float(o[4 * i + 1]) * inv * sc.y);
+            w[2 * i + 1] = pack_out<OUT_DTYPE>(__uint_as_float(o[4 * i + 2]) * inv * sc.z, __uint_as_float(o[4 * i + 3]) * inv * sc.w);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            w[i] = pack_out<OUT_DTYPE>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+        }
         if (store) {
 #pragma unroll
           for (int i = 0; i < 16; i += 4)
@@ -364,7 +388,8 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       }
     }
     if (p.lse != nullptr && store)
-      p.lse[(static_cast<int64_t>(b) * p.heads_q + h) * p.len_q + q_row] = ptx::lg2(d_sum) + m_used;
+      p.lse[(static_cast<int64_t>(b) * p.heads_q + h) * p.len_q + q_row] =
+          ptx::lg2(d_sum) + m_used - (kFp8 ? kLog2Of448 : 0.0f);
   }
   ptx::tc_fence_before();
 }
@@ -373,7 +398,8 @@ template <int D, int PV_MODE, int OUT_DTYPE>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
-  using Plan = SmemPlan<D>;
+  constexpr bool kFp8 = (PV_MODE == SAGE_B200_PV_F8);
+  using Plan = SmemPlan<D, kFp8>;
   constexpr bool kF16Acc = (PV_MODE == SAGE_B200_PV_F16);
   constexpr bool kInstBuf = (PV_MODE == SAGE_B200_PV_F16_F32);
   extern __shared__ uint8_t smem_raw[];
@@ -462,7 +488,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarVFull + vs), Plan::kVBytes);
 #pragma unroll
-        for (int pn = 0; pn < D / 64; ++pn)
+        for (int pn = 0; pn < (kFp8 ? 1 : D / 64); ++pn)      // fp16: 64-channel panels; e4m3: one panel of D bytes
           ptx::tma_load_4d(smem_base + Plan::kVOff + vs * Plan::kVBytes + pn * (kBlockKV * 128), &tm_v,
                            bars + 8 * (kBarVFull + vs), pn * 64, j * kBlockKV, h_kv, b);
       }
@@ -487,14 +513,14 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t k_smem = smem_base + Plan::kKOff;
       const uint32_t v_smem = smem_base + Plan::kVOff;
       const uint32_t idq = idesc_qk();
-      const uint32_t idp = idesc_pv<D, kF16Acc>();
+      const uint32_t idp = kFp8 ? idesc_pv_f8<D>() : idesc_pv<D, kF16Acc>();
       const uint32_t idp_chunk = idesc_pv<64, true>();
 
       // Descriptors differ only in their 14-bit start-address field (units of 16 bytes), which never
       // carries out of the field for shared-memory addresses: build them once, then add offsets.
       const uint64_t q_desc0 = desc_kmajor<kRowBytesQK>(q_smem);
       const uint64_t k_desc0 = desc_kmajor<kRowBytesQK>(k_smem);
-      const uint64_t v_desc0 = desc_mnmajor(v_smem, kBlockKV * 128);
+      const uint64_t v_desc0 = kFp8 ? desc_mnmajor_f8<D>(v_smem) : desc_mnmajor(v_smem, kBlockKV * 128);
 
       auto issue_qk = [&](int t, int stage) {
         const uint32_t d_t = tmem_base + t * 256;
@@ -517,11 +543,18 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t a_t = tmem_base + t * 256;
         const uint64_t db0 = v_desc0 + static_cast<uint64_t>((stage * Plan::kVBytes) >> 4);
         if (ptx::elect_one()) {
+          if constexpr (kFp8) {
 #pragma unroll
-          for (int s = 0; s < kBlockKV / 16; ++s) {
-            // 16 keys per instruction: 8 packed columns of P, 16 rows (2 KB) of every V panel
-            ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 2048) >> 4), idp,
-                            (accumulate || s != 0) ? 1u : 0u);
+            for (int s = 0; s < kBlockKV / 32; ++s)   // 32 keys per instruction: 8 columns of P, 32 rows of V
+              ptx::mma_f8_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 32 * D) >> 4), idp,
+                             (accumulate || s != 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int s = 0; s < kBlockKV / 16; ++s) {
+              // 16 keys per instruction: 8 packed columns of P, 16 rows (2 KB) of every V panel
+              ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 2048) >> 4), idp,
+                              (accumulate || s != 0) ? 1u : 0u);
+            }
           }
         }
         __syncwarp();

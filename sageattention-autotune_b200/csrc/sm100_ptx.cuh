@@ -119,6 +119,18 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem desc], e4m3 x e4m3 -> f32
+__device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // D[tmem] (+)= A[smem desc] * B[smem desc], f16 x f16
 __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                            uint32_t accumulate) {
@@ -207,6 +219,19 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// four fp32 -> packed e4m3x4 (round to nearest, saturating), v0 in the lowest byte
+__device__ __forceinline__ uint32_t pack_e4m3x4(float v0, float v1, float v2, float v3) {
+  uint32_t r;
+  asm("{\n"
+      " .reg .b16 lo, hi;\n"
+      " cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n"
+      " cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n"
+      " mov.b32 %0, {lo, hi};\n"
+      "}"
+      : "=r"(r)
+      : "f"(v0), "f"(v1), "f"(v2), "f"(v3));
   return r;
 }
 // fp32 accumulator + the fp16 value held in the low half of a 32-bit register, one instruction

@@ -17,13 +17,14 @@ F16, BF16 = 0, 1
 GROUP_Q_THREAD, GROUP_K_THREAD, GROUP_BLOCK = 0, 1, 2
 DIV_FULL, DIV_IEEE = 0, 1
 GRAN_PER_THREAD, GRAN_PER_BLOCK = 0, 1
-PV_F32, PV_F16, PV_F16_F32 = 0, 1, 2
+PV_F32, PV_F16, PV_F16_F32, PV_F8 = 0, 1, 2, 3
 
 EXPORTS = (
     "sage_b200_version", "sage_b200_last_error", "sage_b200_mean_k_scratch_bytes", "sage_b200_mean_k",
     "sage_b200_mean_k_static_capacity_bytes", "sage_b200_mean_k_static",
     "sage_b200_quant_int8", "sage_b200_smooth_quant_k_scratch_bytes", "sage_b200_smooth_quant_k",
-    "sage_b200_cast_v_f16", "sage_b200_attn_fwd",
+    "sage_b200_cast_v_f16", "sage_b200_attn_fwd", "sage_b200_quant_v_fp8_scratch_bytes", "sage_b200_quant_v_fp8",
+    "sage_b200_attn_fwd_fp8",
 )
 
 _lib = None
@@ -64,6 +65,13 @@ def lib() -> ctypes.CDLL:
         L.sage_b200_attn_fwd.restype = i
         L.sage_b200_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i,
                                          i64p, i64p, i64p, i64p, i, f, i, i, i, i, i, i, vp]
+        L.sage_b200_quant_v_fp8_scratch_bytes.restype = ctypes.c_size_t
+        L.sage_b200_quant_v_fp8_scratch_bytes.argtypes = [i, i, i, i]
+        L.sage_b200_quant_v_fp8.restype = i
+        L.sage_b200_quant_v_fp8.argtypes = [vp, vp, vp, vp, ctypes.c_size_t, i, i, i, i, i, i64p, i64p, vp]
+        L.sage_b200_attn_fwd_fp8.restype = i
+        L.sage_b200_attn_fwd_fp8.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i,
+                                             i64p, i64p, i64p, i64p, i, f, i, i, i, i, i, vp]
         _lib = L
     return _lib
 

@@ -27,6 +27,7 @@ if DEFAULT_PV_ACCUM_DTYPE not in ("fp32", "fp16", "fp16+fp32"):
     DEFAULT_PV_ACCUM_DTYPE = "fp32"
 
 _PV_CODE = {"fp32": C.PV_F32, "fp16": C.PV_F16, "fp16+fp32": C.PV_F16_F32}
+_FP8_PV = "fp8"      # internal selector of the e4m3 P.V kernel
 
 
 # When set to a list, (label, start_event, end_event) is appended around each group of kernel
@@ -86,11 +87,12 @@ def _lse_correction(q, km, tensor_layout):
 
 
 def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_layout, is_causal, sm_scale,
-                       qk_config, pv_accum_dtype="fp32", return_lse=False, granularity="per_thread"):
+                       qk_config, pv_accum_dtype="fp32", return_lse=False, granularity="per_thread", v_scale=None):
     """The attention core on pre-quantised tensors; the counterpart of
     torch.ops.sageattention_qattn_sm80.qk_int8_sv_f16_accum_*_attn (csrc/qattn/pybind_sm80.cpp:24-98).
     Writes `output` in place and returns the base-2 LSE ((0,)-shaped when not requested)."""
-    if pv_accum_dtype not in _PV_CODE:
+    fp8 = v_scale is not None
+    if not fp8 and pv_accum_dtype not in _PV_CODE:
         raise ValueError("pv_accum_dtype must be 'fp32', 'fp16', or 'fp16+fp32'.")
     b, hq, nq, d = C.bhnd(q_int8, tensor_layout)
     _, hkv, nk, _ = C.bhnd(k_int8, tensor_layout)
@@ -99,16 +101,25 @@ def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_
     lse = torch.empty((b, hq, nq) if return_lse else (0,), dtype=torch.float32, device=dev)
     check = _check_status_enabled()
     status = torch.zeros(4, dtype=torch.int32, device=dev) if check else None
+    gran = C.GRAN_PER_THREAD if granularity == "per_thread" else C.GRAN_PER_BLOCK
     with torch.cuda.device(dev):
-        C.check(C.lib().sage_b200_attn_fwd(
-            q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), output.data_ptr(),
-            q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
-            status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
-            C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
-            C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
-            1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k,
-            C.GRAN_PER_THREAD if granularity == "per_thread" else C.GRAN_PER_BLOCK,
-            _PV_CODE[pv_accum_dtype], C.stream_ptr(dev)))
+        if fp8:
+            C.check(C.lib().sage_b200_attn_fwd_fp8(
+                q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), v_scale.data_ptr(), output.data_ptr(),
+                q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
+                status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
+                C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
+                C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
+                1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran, C.stream_ptr(dev)))
+        else:
+            C.check(C.lib().sage_b200_attn_fwd(
+                q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), output.data_ptr(),
+                q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
+                status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
+                C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
+                C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
+                1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran,
+                _PV_CODE[pv_accum_dtype], C.stream_ptr(dev)))
     if check:
         st = status.tolist()
         if st[0] != 0:
@@ -132,7 +143,7 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         raise ValueError("k and v must have the same shape.")
     if tensor_layout not in ("NHD", "HND"):
         raise ValueError("tensor_layout must be 'NHD' or 'HND'.")
-    if pv_accum_dtype not in _PV_CODE:
+    if pv_accum_dtype not in _PV_CODE and pv_accum_dtype != _FP8_PV:
         raise ValueError("pv_accum_dtype must be 'fp32', 'fp16', or 'fp16+fp32'.")
     if qk_quant_gran not in ("per_thread", "per_block"):
         raise ValueError("qk_quant_gran must be 'per_thread' or 'per_block'.")
@@ -169,13 +180,17 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         else:
             km = None
             k_int8, k_scale = Q._quant_one(k, None, blk_k, k_warp, k_kind, tensor_layout, Q.default_div_mode())
+    v_scale = None
     with _Timed("cast_v"):
-        v_fp16 = cast_v_fp16(v, tensor_layout)
+        if pv_accum_dtype == _FP8_PV:
+            v_fp16, v_scale = Q.quant_v_fp8(v, tensor_layout)
+        else:
+            v_fp16 = cast_v_fp16(v, tensor_layout)
 
     output = torch.empty(q.size(), dtype=dtype, device=q.device)
     with _Timed("attn"):
         lse = attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_layout, is_causal,
-                                 sm_scale, qk_config, pv_accum_dtype, return_lse, qk_quant_gran)
+                                 sm_scale, qk_config, pv_accum_dtype, return_lse, qk_quant_gran, v_scale)
     output = output[..., :head_dim]
     if not return_lse:
         return output
@@ -202,13 +217,29 @@ def sageattn_qk_int8_pv_fp16_cuda(q, k, v, tensor_layout="HND", is_causal=False,
                                 return_lse, qk_config, sm_scale, qk_quant_gran)
 
 
+def sageattn_qk_int8_pv_fp8_cuda(q, k, v, tensor_layout="HND", is_causal=False, qk_quant_gran="per_thread",
+                                 sm_scale: Optional[float] = None, pv_accum_dtype="fp32", smooth_k=True,
+                                 smooth_v=False, return_lse=False, attn_mask=None):
+    """SageAttention forward with fp8 (e4m3) P.V: int8 Q.K^T as in sageattn_qk_int8_pv_fp16_cuda, V
+    quantised to e4m3 with one scale per channel, P rounded to e4m3, fp32 accumulation.  The name is
+    the one the reference exports as a placeholder (core.py:19); the argument list follows upstream
+    SageAttention2's function of that name.  `pv_accum_dtype` other than "fp32" (upstream also has
+    "fp32+fp32" and "fp32+fp16" two-level schemes for sm89/sm90) is accepted and runs as fp32."""
+    assert attn_mask is None
+    if smooth_v:
+        warnings.warn("smooth_v is not built for the fp8 path and will be ignored.", stacklevel=2)
+    kv_len = k.size(2) if tensor_layout == "HND" else k.size(1)
+    qk_config = select_qk_config(_padded_head_dim(q.size(-1)), is_causal, "fp32", kv_len)
+    return _sageattn_configured(q, k, v, tensor_layout, is_causal, _FP8_PV, smooth_k, False, return_lse, qk_config,
+                                sm_scale, qk_quant_gran)
+
+
 C.lib()  # fail at import time if the native library is missing
 
 sageattn = sageattn_qk_int8_pv_fp16_cuda
 
 # Names other libraries probe for (reference: core.py:18-21).  The Triton backend is not part of
-# this package; fp8 PV and varlen are not built yet.
+# this package; the sm90 fp8 variant and varlen are not built.
 sageattn_qk_int8_pv_fp16_triton = None
-sageattn_qk_int8_pv_fp8_cuda = None
 sageattn_qk_int8_pv_fp8_cuda_sm90 = None
 sageattn_varlen = None

@@ -141,3 +141,22 @@ def cast_v_fp16(v: torch.Tensor, tensor_layout: str = "HND") -> torch.Tensor:
             v.data_ptr(), out.data_ptr(), C.dtype_code(v.dtype), b, h, n, d,
             C.bhn_strides(v, tensor_layout), C.bhn_strides(out, tensor_layout), C.stream_ptr(v.device)))
     return out
+
+
+def quant_v_fp8(v: torch.Tensor, tensor_layout: str = "HND"):
+    """(v_fp8, v_scale): V in fp8 e4m3 with one fp32 scale per (batch, head, channel),
+    scale = max|v| over the sequence / 448.  v_fp8 keeps v's shape and dimension order
+    (dtype torch.float8_e4m3fn), v_scale is (batch, heads, head_dim)."""
+    _check_in(v, "v")
+    b, h, n, d = C.bhnd(v, tensor_layout)
+    out = torch.empty(v.shape, dtype=torch.uint8, device=v.device)
+    v_scale = torch.empty((b, h, d), dtype=torch.float32, device=v.device)
+    L = C.lib()
+    nbytes = L.sage_b200_quant_v_fp8_scratch_bytes(b, h, n, d)
+    scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=v.device)
+    with torch.cuda.device(v.device):
+        C.check(L.sage_b200_quant_v_fp8(v.data_ptr(), out.data_ptr(), v_scale.data_ptr(), scratch.data_ptr(),
+                                        scratch.numel() * 4, C.dtype_code(v.dtype), b, h, n, d,
+                                        C.bhn_strides(v, tensor_layout), C.bhn_strides(out, tensor_layout),
+                                        C.stream_ptr(v.device)))
+    return out.view(torch.float8_e4m3fn), v_scale
