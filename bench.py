@@ -154,7 +154,7 @@ def cpu_baseline(w, seconds_hint=20.0):
     ws = dict(w, B=1, Hq=w["Hq"] // w["Hkv"], Hkv=1, N=n)
     q, k, v = make_inputs(ws, 0, 1, "cpu")
     t0 = time.perf_counter()
-    O.sageattn(q, k, v, w["layout"], w["causal"], w["pv"], True)
+    O.sageattn(q, k, v, w["layout"], w["causal"], "fp32" if w["pv"] == "fp8" else w["pv"], True)
     dt = time.perf_counter() - t0
     tops = literal_flops(ws, ws["Hq"]) / dt / 1e12
     sample = f"B=1, {ws['Hq']} q-head(s) on 1 kv-head, N={n}, D={w['D']}, same dtype/causal/pv mode; {dt:.1f} s"
@@ -316,7 +316,7 @@ def main():
         hout = torch.empty(hq.shape, dtype=hq.dtype, pin_memory=True)
 
         def step_host():
-            sageattn_host(hq, hk, hv, out=hout, device=dev, **kw)
+            sageattn_host(hq, hk, hv, out=hout, device=dev, attn_fn=attn_call, **kw)
         e2e_steps = max(2, min(args.steps, 5))
         e2e_ms = timed(step_host, e2e_steps, 1) / e2e_steps
         e2e = {"value": F_lit / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,

@@ -16,9 +16,10 @@ from .parallel import slice_heads
 
 def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
                   tensor_layout: str = "HND", kv_heads_per_chunk: Optional[int] = None,
-                  device: Optional[torch.device] = None, **kwargs) -> torch.Tensor:
+                  device: Optional[torch.device] = None, attn_fn=None, **kwargs) -> torch.Tensor:
     """q, k, v: CPU tensors (pin them for asynchronous copies).  Returns a CPU tensor shaped like q
-    (written into `out` when given).  Extra keyword arguments go to `sageattn`."""
+    (written into `out` when given).  Extra keyword arguments go to `attn_fn` (default `sageattn`)."""
+    attn_fn = sageattn if attn_fn is None else attn_fn
     if q.is_cuda or k.is_cuda or v.is_cuda:
         raise ValueError("sageattn_host takes host tensors; use sageattn for device tensors.")
     if kwargs.get("return_lse"):
@@ -45,7 +46,7 @@ def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Option
                 ready = torch.cuda.Event()
                 ready.record(s_in)
             main.wait_event(ready)
-            o = sageattn(dq, dk, dv, tensor_layout=tensor_layout, **kwargs)
+            o = attn_fn(dq, dk, dv, tensor_layout=tensor_layout, **kwargs)
             for t in (dq, dk, dv):
                 t.record_stream(main)
             done = torch.cuda.Event()

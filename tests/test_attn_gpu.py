@@ -255,3 +255,19 @@ def test_fp8_api_close_to_fp16_pv_and_exact_attention():
     assert c["cos"] >= 0.999 and c["max_abs"] <= 5e-2, c
     assert O.compare(o8.cpu(), exact)["fro_rel"] <= 0.05
     assert float((lse8 - lse16).abs().max()) <= 1e-3
+
+
+def test_sageattn_traces_under_torch_compile():
+    """torch.compile(fullgraph=True) goes through the registered custom op and its fake implementation
+    (the reference tests the same property, tests/test_sageattn_compile.py:21-31)."""
+    import sageattention
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 2, 2, 256, 64, torch.float16, "HND", seed=5)
+
+    def fn(q, k, v):
+        return sageattention.sageattn(q, k, v, tensor_layout="HND", is_causal=True) * 2.0
+
+    compiled = torch.compile(fn, fullgraph=True, backend="aot_eager")
+    got = compiled(q, k, v)
+    exp = fn(q, k, v)
+    assert got.shape == q.shape and torch.allclose(got.float(), exp.float(), atol=1e-3)
