@@ -7,6 +7,7 @@
 #include "attn_common.cuh"
 #include "attn_v1.cuh"
 #include "attn_v2.cuh"
+#include "attn_v3.cuh"
 
 namespace sage {
 
@@ -65,9 +66,24 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   }();
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
   int smem;
-  if constexpr (PV_MODE == SAGE_B200_PV_F16_F32 || PV_MODE == SAGE_B200_PV_F8) {
+  if constexpr (PV_MODE == SAGE_B200_PV_F16_F32) {
+    // the two-level accumulate mode has its own pipeline: one tile per CTA, fold warpgroup
+    // (SAGE_B200_KERNEL=coupled keeps the two-tile kernel that folds inside the softmax warps)
+    static const bool two_tile = [] {
+      const char* e = getenv("SAGE_B200_KERNEL");
+      return e != nullptr && e[0] == 'c';
+    }();
+    if (two_tile) {
+      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
+      smem = v1::SmemPlan<D>::kDynamic;
+    } else {
+      kern = v3::sage_attn_fwd_kernel<D, OUT_DTYPE>;
+      smem = v3::SmemPlan<D>::kDynamic;
+      grid.x = (p.len_q + kTileQ - 1) / kTileQ;
+    }
+  } else if constexpr (PV_MODE == SAGE_B200_PV_F8) {
     kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
-    smem = v1::SmemPlan<D, PV_MODE == SAGE_B200_PV_F8>::kDynamic;
+    smem = v1::SmemPlan<D, true>::kDynamic;
   } else {
     kern = force_v1 ? v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE> : v2::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
     smem = force_v1 ? v1::SmemPlan<D>::kDynamic : v2::SmemPlan<D>::kDynamic;
@@ -76,7 +92,7 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   // the attribute is per device: set it for every device that launches
   static bool done[2][64] = {};
   static std::mutex mu;
-  const int which = (kern == v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>) ? 0 : 1;
+  const int which = (kern == v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>) ? 0 : 1;   // v2 and v3 never share a PV_MODE
   int dev = 0;
   SAGE_CUDA_TRY(cudaGetDevice(&dev));
   {
