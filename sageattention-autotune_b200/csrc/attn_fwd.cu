@@ -66,6 +66,7 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   }();
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
   int smem;
+  int threads = kAttnThreads;
   if constexpr (PV_MODE == SAGE_B200_PV_F16_F32) {
     // the two-level accumulate mode has its own pipeline: one tile per CTA, fold warpgroup
     // (SAGE_B200_KERNEL=coupled keeps the two-tile kernel that folds inside the softmax warps)
@@ -80,6 +81,7 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       kern = v3::sage_attn_fwd_kernel<D, OUT_DTYPE>;
       smem = v3::SmemPlan<D>::kDynamic;
       grid.x = (p.len_q + kTileQ - 1) / kTileQ;
+      threads = v3::kThreads;
     }
   } else if constexpr (PV_MODE == SAGE_B200_PV_F8) {
     kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
@@ -104,7 +106,7 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       if (dev >= 0 && dev < 64) done[which][dev] = true;
     }
   }
-  kern<<<grid, kAttnThreads, smem, stream>>>(mq, mk, mv, p);
+  kern<<<grid, threads, smem, stream>>>(mq, mk, mv, p);
   SAGE_CUDA_TRY(cudaGetLastError());
   return SAGE_B200_OK;
 }
@@ -156,6 +158,8 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   SAGE_REQUIRE((pv_accum == SAGE_B200_PV_F8) == (v_scale != nullptr),
                "attn_fwd: the fp8 mode (and only it) takes a v_scale; use sage_b200_attn_fwd_fp8");
   SAGE_REQUIRE(v_scale == nullptr || aligned16(v_scale), "attn_fwd: v_scale must be 16-byte aligned");
+  SAGE_REQUIRE(granularity != SAGE_B200_GRAN_PER_THREAD || aligned16(k_scale),
+               "attn_fwd: per-thread k_scale must be 16-byte aligned (it is read four groups at a time)");
   if (head_dim != 64 && head_dim != 128) {
     if (head_dim == 256)
       return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: head_dim 256 is not built yet");

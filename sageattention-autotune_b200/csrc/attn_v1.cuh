@@ -98,23 +98,43 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
   float m_used = -INFINITY;    // reference point P and O are expressed against
   float d_sum = 0.0f;
   bool ok = true;
+  // scales of the two 64-key halves of block j (vector loads: the groups of one half are contiguous)
+  const bool per_thread = (p.gran == SAGE_B200_GRAN_PER_THREAD);
+  auto load_scales = [&](int j, float4& lo, float4& hi) {
+    lo = make_float4(0.f, 0.f, 0.f, 0.f);
+    hi = lo;
+    if (per_thread) {
+      if (j * 8 + 3 < p.k_groups)
+        asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "l"(ks_base + 8 * j));
+      if (j * 8 + 7 < p.k_groups)
+        asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w) : "l"(ks_base + 8 * j + 4));
+    } else {
+      if (2 * j < p.k_groups) {
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(lo.x) : "l"(ks_base + 2 * j));
+        lo.y = lo.z = lo.w = lo.x;
+      }
+      if (2 * j + 1 < p.k_groups) {
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(hi.x) : "l"(ks_base + 2 * j + 1));
+        hi.y = hi.z = hi.w = hi.x;
+      }
+    }
+  };
 
 #pragma unroll 1
   for (int j = 0; j < n_blocks; ++j) {
     const int k0 = j * kBlockKV;
-    // the eight dequantisation constants of this block
+    // the eight dequantisation constants of this block; the next block's line is pulled into L1 now
+    // so that its loads do not pay an L2 round trip (registers are too scarce to hold them a block ahead)
     float a[8];
-    if (p.gran == SAGE_B200_GRAN_PER_THREAD) {
-#pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const int g = j * 8 + t;
-        a[t] = (g < p.k_groups) ? __ldg(ks_base + g) : 0.0f;
-      }
-    } else {
-      const float s0 = (2 * j < p.k_groups) ? __ldg(ks_base + 2 * j) : 0.0f;
-      const float s1 = (2 * j + 1 < p.k_groups) ? __ldg(ks_base + 2 * j + 1) : 0.0f;
-#pragma unroll
-      for (int t = 0; t < 4; ++t) { a[t] = s0; a[4 + t] = s1; }
+    {
+      float4 lo, hi;
+      load_scales(j, lo, hi);
+      if (j + 1 < n_blocks)
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(ks_base + (per_thread ? 8 : 2) * (j + 1)));
+      a[0] = lo.x, a[1] = lo.y, a[2] = lo.z, a[3] = lo.w;
+      a[4] = hi.x, a[5] = hi.y, a[6] = hi.z, a[7] = hi.w;
     }
 #pragma unroll
     for (int t = 0; t < 8; ++t) a[t] = p.scale_log2 * (q_sc * a[t]);
