@@ -34,10 +34,29 @@ struct AttnParams {
   int causal;
   float scale_log2;              // sm_scale * log2(e)
   int64_t os_b, os_h, os_n;
+  unsigned long long launch_id;  // non-zero, unique per launch of this process (see g_attn_abort_id)
 #ifdef SAGE_TRACE
   long long* trace;              // debug builds only: per-role event timestamps of one CTA
 #endif
 };
+
+// Identifier of the last launch in which a bounded wait ran out.  A CTA that starts after that
+// returns at once, so a launch whose pipeline is stuck ends after one wait period instead of one
+// period per wave of CTAs, whether or not the caller passed a status word.
+static __device__ unsigned long long g_attn_abort_id = 0;
+
+__device__ __forceinline__ bool launch_aborted(const AttnParams& p) {
+  if (*reinterpret_cast<volatile unsigned long long*>(&g_attn_abort_id) == p.launch_id) return true;
+  return p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0;
+}
+__device__ __forceinline__ void publish_abort(const AttnParams& p, int code) {
+  *reinterpret_cast<volatile unsigned long long*>(&g_attn_abort_id) = p.launch_id;
+  if (p.status != nullptr && atomicCAS(p.status, 0, code) == 0) {
+    p.status[1] = blockIdx.x;
+    p.status[2] = blockIdx.y;
+    p.status[3] = blockIdx.z;
+  }
+}
 
 #ifdef SAGE_TRACE
 // role r writes (event << 56 | j << 40 | clock) into trace[r * 8192 + n]; slot 0 holds n

@@ -1,6 +1,7 @@
 // Host side of the attention core: argument checks, TMA tensor maps, kernel selection.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -8,6 +9,7 @@
 #include "attn_v1.cuh"
 #include "attn_v2.cuh"
 #include "attn_v3.cuh"
+#include "attn_v4.cuh"
 
 namespace sage {
 
@@ -67,6 +69,7 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
   int smem;
   int threads = kAttnThreads;
+  int which = 1;               // index of the kernel family in the per-device attribute cache below
   if constexpr (PV_MODE == SAGE_B200_PV_F16_F32) {
     // the two-level accumulate mode has its own pipeline: one tile per CTA, fold warpgroup
     // (SAGE_B200_KERNEL=coupled keeps the two-tile kernel that folds inside the softmax warps)
@@ -74,9 +77,21 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       const char* e = getenv("SAGE_B200_KERNEL");
       return e != nullptr && e[0] == 'c';
     }();
+    static const bool paired = [] {
+      const char* e = getenv("SAGE_B200_KERNEL");
+      return e != nullptr && e[0] == 'p';
+    }();
     if (two_tile) {
       kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
       smem = v1::SmemPlan<D>::kDynamic;
+    } else if (!paired) {
+      // two independent softmax warpgroups on alternating blocks (SAGE_B200_KERNEL=paired selects the
+      // variant with two threads per row)
+      kern = v4::sage_attn_fwd_kernel<D, OUT_DTYPE>;
+      smem = v4::SmemPlan<D>::kDynamic;
+      grid.x = (p.len_q + kTileQ - 1) / kTileQ;
+      threads = v4::kThreads;
+      which = 2;
     } else {
       kern = v3::sage_attn_fwd_kernel<D, OUT_DTYPE>;
       smem = v3::SmemPlan<D>::kDynamic;
@@ -92,9 +107,9 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   }
   cudaError_t attr_err = cudaSuccess;
   // the attribute is per device: set it for every device that launches
-  static bool done[2][64] = {};
+  static bool done[3][64] = {};
   static std::mutex mu;
-  const int which = (kern == v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>) ? 0 : 1;   // v2 and v3 never share a PV_MODE
+  if (which == 1 && kern == v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>) which = 0;   // v2 and v3 never share a PV_MODE
   int dev = 0;
   SAGE_CUDA_TRY(cudaGetDevice(&dev));
   {
@@ -183,6 +198,8 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   p.out = out;
   p.lse = lse;
   p.status = status;
+  static std::atomic<unsigned long long> next_launch_id{1};
+  p.launch_id = next_launch_id.fetch_add(1, std::memory_order_relaxed);
   p.len_q = len_q;
   p.len_kv = len_kv;
   p.heads_q = heads_q;

@@ -390,7 +390,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int q0 = pair * 2 * kTileQ;
 
   // another CTA of this launch already gave up: do not queue more bounded waits behind it
-  if (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
+  if (launch_aborted(p)) return;
 
   int n_steps[2];
 #pragma unroll
@@ -593,13 +593,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   if (warp == 8) ptx::tmem_dealloc(tmem_base, 512);
-  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) {
-    if (atomicCAS(p.status, 0, *abort_flag) == 0) {
-      p.status[1] = blockIdx.x;
-      p.status[2] = blockIdx.y;
-      p.status[3] = blockIdx.z;
-    }
-  }
+  if (threadIdx.x == 0 && *abort_flag != 0) publish_abort(p, *abort_flag);
 }
 
 }  // namespace v2

@@ -181,6 +181,30 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[N]
       ::SAGE_W32(r, OFF), "r"(taddr)
       : "memory");
 }
+// 16-column variants for roles that run on a small register budget
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(OFF + 16 <= N, "register window out of range");
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]), "=r"(r[OFF + 5]),
+        "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]), "=r"(r[OFF + 10]),
+        "=r"(r[OFF + 11]), "=r"(r[OFF + 12]), "=r"(r[OFF + 13]), "=r"(r[OFF + 14]), "=r"(r[OFF + 15])
+      : "r"(taddr)
+      : "memory");
+}
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[N]) {
+  static_assert(OFF + 16 <= N, "register window out of range");
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::"r"(r[OFF + 0]), "r"(r[OFF + 1]), "r"(r[OFF + 2]), "r"(r[OFF + 3]), "r"(r[OFF + 4]), "r"(r[OFF + 5]),
+        "r"(r[OFF + 6]), "r"(r[OFF + 7]), "r"(r[OFF + 8]), "r"(r[OFF + 9]), "r"(r[OFF + 10]), "r"(r[OFF + 11]),
+        "r"(r[OFF + 12]), "r"(r[OFF + 13]), "r"(r[OFF + 14]), "r"(r[OFF + 15]), "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -235,6 +259,19 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float v0, float v1, float v2, fl
   return r;
 }
 // fp32 accumulator + the fp16 value held in the low half of a 32-bit register, one instruction
+// a (fp16, low half of `packed`) * b (fp16, low half of `b16`) + acc in one mixed-precision FMA
+__device__ __forceinline__ float fma_f32_f16lo(uint32_t packed, uint32_t b16, float acc) {
+  float r;
+  asm("{\n"
+      " .reg .b16 lo, hi, bl, bh;\n"
+      " mov.b32 {lo, hi}, %1;\n"
+      " mov.b32 {bl, bh}, %2;\n"
+      " fma.rn.f32.f16 %0, lo, bl, %3;\n"
+      "}"
+      : "=f"(r)
+      : "r"(packed), "r"(b16), "f"(acc));
+  return r;
+}
 __device__ __forceinline__ float add_f32_f16lo(float acc, uint32_t packed) {
   float r;
   asm("{\n"
