@@ -7,8 +7,6 @@
 
 #include "attn_common.cuh"
 #include "attn_v1.cuh"
-#include "attn_v2.cuh"
-#include "attn_v3.cuh"
 #include "attn_v4.cuh"
 
 namespace sage {
@@ -58,58 +56,41 @@ static int make_map(CUtensorMap* map, const void* base, int elem_bytes, int batc
 template <int D, int PV_MODE, int OUT_DTYPE>
 static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                        dim3 grid, cudaStream_t stream) {
-  // Two pipelines exist.  The coupled one (128-key steps, one score buffer per tile) is the default:
-  // it measures fastest on B200 because the softmax warps are bound by instruction issue, and it
-  // pays the fixed per-step cost half as often.  "fp16+fp32" needs its spare score columns and always
-  // runs it.  SAGE_B200_KERNEL=decoupled selects the double-buffered 64-key pipeline for the others.
-  static const bool force_v1 = [] {
-    const char* e = getenv("SAGE_B200_KERNEL");
-    return !(e != nullptr && e[0] == 'd');
-  }();
+  // Two kernels exist.  fp32, fp16 and fp8 accumulation run the two-tile kernel (attn_v1.cuh: 256 query
+  // rows per CTA share every K/V block, the output accumulates in tensor memory).  The two-level
+  // "fp16+fp32" mode needs an fp16 partial product next to the scores and runs the one-tile kernel with
+  // a fold warpgroup (attn_v4.cuh); SAGE_B200_KERNEL=coupled runs it on the two-tile kernel instead,
+  // which folds inside the softmax warps (slower, kept as a cross-check).
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
   int smem;
   int threads = kAttnThreads;
-  int which = 1;               // index of the kernel family in the per-device attribute cache below
+  int which = 0;               // index of the kernel in the per-device attribute cache below
   if constexpr (PV_MODE == SAGE_B200_PV_F16_F32) {
-    // the two-level accumulate mode has its own pipeline: one tile per CTA, fold warpgroup
-    // (SAGE_B200_KERNEL=coupled keeps the two-tile kernel that folds inside the softmax warps)
     static const bool two_tile = [] {
       const char* e = getenv("SAGE_B200_KERNEL");
       return e != nullptr && e[0] == 'c';
     }();
-    static const bool paired = [] {
-      const char* e = getenv("SAGE_B200_KERNEL");
-      return e != nullptr && e[0] == 'p';
-    }();
     if (two_tile) {
       kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
       smem = v1::SmemPlan<D>::kDynamic;
-    } else if (!paired) {
-      // two independent softmax warpgroups on alternating blocks (SAGE_B200_KERNEL=paired selects the
-      // variant with two threads per row)
+    } else {
       kern = v4::sage_attn_fwd_kernel<D, OUT_DTYPE>;
       smem = v4::SmemPlan<D>::kDynamic;
       grid.x = (p.len_q + kTileQ - 1) / kTileQ;
       threads = v4::kThreads;
-      which = 2;
-    } else {
-      kern = v3::sage_attn_fwd_kernel<D, OUT_DTYPE>;
-      smem = v3::SmemPlan<D>::kDynamic;
-      grid.x = (p.len_q + kTileQ - 1) / kTileQ;
-      threads = v3::kThreads;
+      which = 1;
     }
   } else if constexpr (PV_MODE == SAGE_B200_PV_F8) {
     kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
     smem = v1::SmemPlan<D, true>::kDynamic;
   } else {
-    kern = force_v1 ? v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE> : v2::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
-    smem = force_v1 ? v1::SmemPlan<D>::kDynamic : v2::SmemPlan<D>::kDynamic;
+    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
+    smem = v1::SmemPlan<D>::kDynamic;
   }
   cudaError_t attr_err = cudaSuccess;
   // the attribute is per device: set it for every device that launches
-  static bool done[3][64] = {};
+  static bool done[2][64] = {};
   static std::mutex mu;
-  if (which == 1 && kern == v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>) which = 0;   // v2 and v3 never share a PV_MODE
   int dev = 0;
   SAGE_CUDA_TRY(cudaGetDevice(&dev));
   {

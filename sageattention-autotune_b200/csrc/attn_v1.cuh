@@ -1,4 +1,4 @@
-// Coupled-pipeline variant of the SageAttention core for B200 (sm_100a): int8 Q.K^T and fp16 P.V on tcgen05 tensor cores with
+// Two-tile kernel of the SageAttention core for B200 (sm_100a): int8 Q.K^T and fp16 (or fp8) P.V on tcgen05 tensor cores with
 // accumulators in tensor memory, TMA-staged operands, online softmax in two softmax warpgroups.
 //
 // It replaces the reference's qk_int8_sv_f16_attn_kernel
@@ -250,9 +250,13 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     // Of every kPolyDen groups of four columns, kPolyNum evaluate 2^x with a polynomial on the FMA pipe
     // and the rest with ex2.approx on the special-function unit, so that both pipes work: measured
     // at N = 32768 the fp32 mode takes 14.6 ms with 0/8, 12.95 ms with 3/8, 13.8 ms with 4/8, 19 ms with
-    // 8/8; the fp16+fp32 mode is bound by its hand-over chain and is indifferent (2/8 kept).
+    // 8/8 (first launches; once the 1000 W power cap lowers the clock: 15.3 / 14.7 ms with 0/8 / 3/8);
+    // the fp16+fp32 mode of this kernel is bound by its hand-over chain and is indifferent (2/8 kept).
     constexpr int kPolyDen = 8;
-    constexpr int kPolyNum = kInstBuf ? 2 : 3;
+#ifndef SAGE_V1_POLY
+#define SAGE_V1_POLY 3
+#endif
+    constexpr int kPolyNum = kInstBuf ? 2 : SAGE_V1_POLY;
     if (!need_mask) {
       // p = 2^(X*a + neg) with neg = -(1.5*2^23*a + m); two columns of one class per packed FMA
       unsigned long long a2[8], neg2[8];

@@ -1,18 +1,23 @@
-// SageAttention core for B200 (sm_100a), pipeline for the two-level "fp16+fp32" accumulate mode with
-// two INDEPENDENT softmax warpgroups on one query tile.
+// SageAttention core for B200 (sm_100a), kernel for the two-level "fp16+fp32" accumulate mode.
 //
 // Semantics of the mode (reference: compute_fp16_sv_permuted_inst_buf, csrc/qattn/attn_utils.cuh:447-518):
 // each block's P.V is accumulated in fp16 starting from zero, and that partial product is then added
 // into an fp32 running output.  An fp16 accumulator in tensor memory takes one column per element, so
-// one 128-row query tile per CTA uses all 512 columns: two score buffers S0/S1 (P overwrites the first
-// 64 columns of its buffer), the fp16 partial product T, and the fp32 output O.  Roles:
-//   warps 0-3   softmax warpgroup A: blocks 0, 2, 4, ... in S0 (thread t = query row t, all 128 keys)
-//   warps 4-7   softmax warpgroup B: blocks 1, 3, 5, ... in S1
-//   warps 8-11  fold warpgroup (thread t = query row t): O = O * alpha + float(T) * beta after every
-//               block, final normalisation and the output store
-//   warp  12    TMA producer (one lane), owner of the TMEM allocation
+// one 128-row query tile per CTA fills the 512 columns: three score buffers S0..S2 (block j lives in
+// S[j % 3]; its P overwrites the first 64 columns) and the fp16 partial product T.  The fp32 output
+// never enters tensor memory: it lives in the registers of the fold warps.  Roles:
+//   warps 0-3   softmax warpgroup A: blocks 0, 2, 4, ... (thread t = query row t, all 128 keys)
+//   warps 4-7   softmax warpgroup B: blocks 1, 3, 5, ...
+//   warps 8-11  fold warpgroup (thread t = query row t, holds that row of O): after every block
+//               O = O * alpha + float(T) * beta; final normalisation and the output store
+//   warp  12    TMA producer (one lane; also stages each block's K scales), owner of the TMEM allocation
 //   warp  13    MMA issuer (whole warp runs the loop, one elected lane issues)
 //   warps 14-15 idle (they only give their registers away)
+// With three score buffers Q.K^T of block j+3 is issued right after P.V of block j, so a softmax
+// warpgroup finds its next scores waiting; the only serial chain left is P.V(j) -> fold(j) -> P.V(j+1)
+// on the single T, which is shorter than a block's softmax.
+// A softmax thread reads its scores twice, 64 columns at a time (pass 1: maximum, pass 2: exponentials),
+// instead of holding 128 of them: that keeps it at 144 registers and leaves 184 for a fold thread.
 // The two softmax warpgroups never wait for one another: each keeps its own reference exponent and row
 // sum.  A reference is an INTEGER r >= the running maximum of the blocks its warpgroup has seen, so
 // P = 2^(s - r) <= 1 as the fp16 partial product requires, and every factor between two references
@@ -22,7 +27,7 @@
 // that the common case a warpgroup also folds the other's last published reference into its own
 // (an unsynchronised read: any earlier value is equally valid).  The two row sums are combined at the end.
 // Because the warpgroups are out of phase, one's tensor-memory and barrier latencies hide behind the
-// other's exponentials; the variant with two threads per row (attn_v3.cuh) stalls both at once.
+// other's exponentials.
 #pragma once
 
 #include "attn_common.cuh"
@@ -34,7 +39,7 @@ constexpr int kRefRing = 4;        // block references in flight between the sof
 constexpr int kScaleRing = 8;      // K dequantisation scales staged by the producer, one slot per block
 constexpr int kThreads = 512;
 // setmaxnreg is a warpgroup-wide instruction: the four warps of a group must ask for the same count
-constexpr int kRegsSoftmax = 208, kRegsFold = 56, kRegsIssue = 40;
+constexpr int kRegsSoftmax = 144, kRegsFold = 184, kRegsIssue = 40;
 static_assert(8 * kRegsSoftmax + 4 * kRegsFold + 4 * kRegsIssue <= 2048, "register file");
 
 enum BarIdx {
@@ -43,11 +48,11 @@ enum BarIdx {
   kBarKEmpty = kBarKFull + kKStages,
   kBarVFull = kBarKEmpty + kKStages,      // kVStages
   kBarVEmpty = kBarVFull + kVStages,
-  kBarSFull = kBarVEmpty + kVStages,      // [buffer] = 2
-  kBarPFull = kBarSFull + 2,              // [buffer] = 2, 128 arrivals
-  kBarTFull = kBarPFull + 2,              // [slot] = 2: a 64-channel unit of P.V has retired
-  kBarTFree = kBarTFull + 2,              // [slot] = 2: the fold has consumed the unit, 128 arrivals
-  kBarStats = kBarTFree + 2,              // warpgroup A published 1/sum, 128 arrivals, single phase
+  kBarSFull = kBarVEmpty + kVStages,      // [buffer] = 3
+  kBarPFull = kBarSFull + 3,              // [buffer] = 3, 128 arrivals
+  kBarTFull = kBarPFull + 3,              // P.V of a block has retired
+  kBarTFree = kBarTFull + 1,              // the fold has consumed T, 128 arrivals
+  kBarStats = kBarTFree + 1,              // warpgroup A published 1/sum, 128 arrivals, single phase
   kBarSum = kBarStats + 1,                // both warpgroups finished, 256 arrivals, single phase
   kBarDrain = kBarSum + 1,
   kNumBars = kBarDrain + 1
@@ -89,7 +94,6 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
                                              volatile float* ref_pub, float* sum_xchg, const float* k_scales,
                                              int wg, int row, int n_blocks, int q_row0, int b, int h) {
   const uint32_t lane_base = static_cast<uint32_t>(row & ~31) << 16;
-  const uint32_t t_s = tmem_base + lane_base + wg * 128;
   const int q_row = q_row0 + row;
   float q_sc;
   {
@@ -112,8 +116,10 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 #pragma unroll 1
   for (int j = wg; j < n_blocks; j += 2) {
     const int k0 = j * kBlockKV;
+    const int buf = j % 3;
+    const uint32_t t_s = tmem_base + lane_base + buf * 128;
     V4_PH(0);
-    ok = wait_bar_warp(bars + 8 * (kBarSFull + wg), (j >> 1) & 1, abort_flag, 10 + wg);
+    ok = wait_bar_warp(bars + 8 * (kBarSFull + buf), (j / 3) & 1, abort_flag, 10 + wg);
     if (!ok) break;
     ptx::tc_fence_after();
     V4_PH(1);
@@ -127,49 +133,46 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       a[4] = qs * hi.x, a[5] = qs * hi.y, a[6] = qs * hi.z, a[7] = qs * hi.w;
     }
 
-    uint32_t s[128];
-    ptx::tmem_ld32<0>(t_s + 0, s);
-    ptx::tmem_ld32<32>(t_s + 32, s);
-    ptx::tmem_ld32<64>(t_s + 64, s);
-    ptx::tmem_ld32<96>(t_s + 96, s);
-    ptx::tmem_wait_ld();
-
     const bool need_mask = (k0 + kBlockKV > p.len_kv) || (p.causal && (k0 + kBlockKV - 1 > q_row0));
+    const int lim = min(p.causal ? (q_row - k0) : kBlockKV, p.len_kv - k0 - 1);   // columns <= lim are visible
+
+    // pass 1: the block maximum, 64 columns at a time (the scores stay in tensor memory and are read
+    // again in pass 2: holding all 128 would cost the registers the fold warps need for O)
     float m_blk = -INFINITY;
-    if (!need_mask) {
-      // X = float(S) + 1.5*2^23 without a conversion (|S| < 2^22); X is monotonic in S, so the class
-      // maxima are taken on X with three-input max and mapped back through the class's constant
+#pragma unroll 1
+    for (int hf = 0; hf < 2; ++hf) {
+      uint32_t s[64];
+      ptx::tmem_ld32<0>(t_s + hf * 64, s);
+      ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
+      ptx::tmem_wait_ld();
+      if (!need_mask) {
+        // per scale class: integer maximum (three-input), then one conversion and one multiply
 #pragma unroll
-      for (int c = 0; c < 128; ++c) s[c] += kMagicI;
+        for (int t = 0; t < 4; ++t) {                       // the class owns columns 2t + 8i, 2t + 8i + 1
+          int v[16];
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const int base = (t >> 2) * 64 + (t & 3) * 2;       // the class owns columns base + 8i, base + 8i + 1
-        float v[16];
+          for (int i = 0; i < 8; ++i) {
+            v[2 * i] = static_cast<int>(s[2 * t + 8 * i]);
+            v[2 * i + 1] = static_cast<int>(s[2 * t + 8 * i + 1]);
+          }
+          int mx = v[0];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[2 * i] = __uint_as_float(s[base + 8 * i]);
-          v[2 * i + 1] = __uint_as_float(s[base + 8 * i + 1]);
+          for (int i = 1; i < 15; i += 2) mx = __vimax3_s32(mx, v[i], v[i + 1]);
+          mx = max(mx, v[15]);
+          const float at = hf ? a[4 + t] : a[t];
+          m_blk = fmaxf(m_blk, static_cast<float>(mx) * at);
         }
-        float mx = v[0];
+      } else {
 #pragma unroll
-        for (int i = 1; i < 15; i += 2) mx = ptx::max3(mx, v[i], v[i + 1]);
-        mx = fmaxf(mx, v[15]);
-        m_blk = fmaxf(m_blk, (mx - kMagicF) * a[t]);
-      }
-    } else {
-      // diagonal or ragged block: scale first, mask to -inf, keep the scaled values in place
-      const int lim_causal = p.causal ? (q_row - k0) : kBlockKV;     // columns <= lim are visible
-      const int lim = min(lim_causal, p.len_kv - k0 - 1);
-#pragma unroll
-      for (int c = 0; c < 128; ++c) {
-        float x = static_cast<float>(static_cast<int>(s[c])) * a[k_class(c)];
-        x = (c <= lim) ? x : -INFINITY;
-        m_blk = fmaxf(m_blk, x);
-        s[c] = __float_as_uint(x);
+        for (int c = 0; c < 64; ++c) {
+          const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
+          const float x = static_cast<float>(static_cast<int>(s[c])) * at;
+          m_blk = fmaxf(m_blk, (hf * 64 + c <= lim) ? x : -INFINITY);
+        }
       }
     }
-
     V4_PH(2);
+
     // new reference: integer, at least this block's maximum, never below anything already used or
     // published by the other warpgroup (whatever value of it this read happens to see)
     const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk)), ref_pub[(wg ^ 1) * kTileQ + row]);
@@ -180,60 +183,77 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     ref_pub[wg * kTileQ + row] = r_new;
     ref_ring[(j % kRefRing) * kTileQ + row] = r_new;      // (slot reuse: block j-4 was folded before S(j) existed)
 
+    // pass 2: P = 2^(S*a - ref), packed to fp16 pairs; the P of keys [64 hf, 64 hf + 64) overwrites
+    // score columns [32 hf, 32 hf + 32), which pass 2 has already consumed
     float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
-    constexpr int kPolyDen = 8, kPolyNum = 3;    // share of 2^x evaluated on the FMA pipe (see attn_v1.cuh)
-    if (!need_mask) {
-      unsigned long long a2[8], neg2[8];
+    // Share of 2^x evaluated with a polynomial on the FMA pipe instead of ex2.approx.  Here 0 is best
+    // (N = 32768 causal, sustained: 18.1 ms with 0/8, 18.4 with 1/8, 18.9 with 2/8, 19.6 with 3/8): with
+    // two warpgroups out of phase the special-function unit is not the limiter and the extra
+    // instructions only cost power.  The two-tile kernel (attn_v1.cuh) is issue-bound and keeps 3/8.
+#ifndef SAGE_V4_POLY
+#define SAGE_V4_POLY 0
+#endif
+    constexpr int kPolyDen = 8, kPolyNum = SAGE_V4_POLY;
+#pragma unroll 1
+    for (int hf = 0; hf < 2; ++hf) {
+      uint32_t s[64];
+      ptx::tmem_ld32<0>(t_s + hf * 64, s);
+      ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
+      ptx::tmem_wait_ld();
+      if (!need_mask) {
+        // X = float(S) + 1.5*2^23 without a conversion (|S| < 2^22), then p = 2^(X*a + neg) with
+        // neg = -(1.5*2^23*a + ref); two columns of one class per packed FMA
+        unsigned long long a2[4], neg2[4];
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const float ng = fmaf(-kMagicF, a[t], -m_ref);
-        a2[t] = ptx::pack2(a[t], a[t]);
-        neg2[t] = ptx::pack2(ng, ng);
-      }
-      unsigned long long acc0 = ptx::pack2(0.0f, 0.0f), acc1 = acc0;
-#pragma unroll
-      for (int c = 0; c < 128; c += 4) {
-        const unsigned long long e0 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 0]), __uint_as_float(s[c + 1])),
-                                                a2[k_class(c)], neg2[k_class(c)]);
-        const unsigned long long e1 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])),
-                                                a2[k_class(c + 2)], neg2[k_class(c + 2)]);
-        float p0, p1, p2, p3;
-        if (((c >> 2) % kPolyDen) < kPolyNum) {
-          ptx::exp2_pair_poly(e0, p0, p1);
-          ptx::exp2_pair_poly(e1, p2, p3);
-        } else {
-          float x0, x1, x2, x3;
-          ptx::unpack2(e0, x0, x1);
-          ptx::unpack2(e1, x2, x3);
-          p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
+        for (int t = 0; t < 4; ++t) {
+          const float at = hf ? a[4 + t] : a[t];
+          const float ng = fmaf(-kMagicF, at, -m_ref);
+          a2[t] = ptx::pack2(at, at);
+          neg2[t] = ptx::pack2(ng, ng);
         }
-        acc0 = ptx::add2(acc0, ptx::pack2(p0, p1));
-        acc1 = ptx::add2(acc1, ptx::pack2(p2, p3));
-        s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
-        s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
-      }
-      ptx::unpack2(acc0, sum0, sum1);
-      ptx::unpack2(acc1, sum2, sum3);
-    } else {
+        unsigned long long acc0 = ptx::pack2(sum0, sum1), acc1 = ptx::pack2(sum2, sum3);
 #pragma unroll
-      for (int c = 0; c < 128; c += 4) {
-        const float p0 = ptx::ex2(__uint_as_float(s[c + 0]) - m_ref);
-        const float p1 = ptx::ex2(__uint_as_float(s[c + 1]) - m_ref);
-        const float p2 = ptx::ex2(__uint_as_float(s[c + 2]) - m_ref);
-        const float p3 = ptx::ex2(__uint_as_float(s[c + 3]) - m_ref);
-        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-        s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
-        s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
+        for (int c = 0; c < 64; c += 4) {
+          const unsigned long long e0 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 0] + kMagicI), __uint_as_float(s[c + 1] + kMagicI)),
+                                                  a2[(c & 7) >> 1], neg2[(c & 7) >> 1]);
+          const unsigned long long e1 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 2] + kMagicI), __uint_as_float(s[c + 3] + kMagicI)),
+                                                  a2[((c + 2) & 7) >> 1], neg2[((c + 2) & 7) >> 1]);
+          float p0, p1, p2, p3;
+          if (((c >> 2) % kPolyDen) < kPolyNum) {
+            ptx::exp2_pair_poly(e0, p0, p1);
+            ptx::exp2_pair_poly(e1, p2, p3);
+          } else {
+            float x0, x1, x2, x3;
+            ptx::unpack2(e0, x0, x1);
+            ptx::unpack2(e1, x2, x3);
+            p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
+          }
+          acc0 = ptx::add2(acc0, ptx::pack2(p0, p1));
+          acc1 = ptx::add2(acc1, ptx::pack2(p2, p3));
+          s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
+          s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
+        }
+        ptx::unpack2(acc0, sum0, sum1);
+        ptx::unpack2(acc1, sum2, sum3);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
+          const float x0 = static_cast<float>(static_cast<int>(s[c + 0])) * at;
+          const float x1 = static_cast<float>(static_cast<int>(s[c + 1])) * at;
+          const float p0 = (hf * 64 + c <= lim) ? ptx::ex2(x0 - m_ref) : 0.0f;
+          const float p1 = (hf * 64 + c + 1 <= lim) ? ptx::ex2(x1 - m_ref) : 0.0f;
+          sum0 += p0;
+          sum1 += p1;
+          s[c / 2] = ptx::pack_f16x2(p0, p1);
+        }
       }
+      ptx::tmem_st32<0>(t_s + hf * 32, s);
     }
     d_sum = d_sum * shrink + ((sum0 + sum1) + (sum2 + sum3));
-
-    // P of this block: 64 packed columns at the start of the score buffer
-    ptx::tmem_st32<0>(t_s + 0, s);
-    ptx::tmem_st32<32>(t_s + 32, s);
     ptx::tmem_wait_st();
     ptx::tc_fence_before();
-    ptx::mbar_arrive(bars + 8 * (kBarPFull + wg));        // also publishes ref_ring (release)
+    ptx::mbar_arrive(bars + 8 * (kBarPFull + buf));       // also publishes ref_ring (release)
     V4_PH(3);
   }
 #ifdef SAGE_TRACE
@@ -265,9 +285,10 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
                                           volatile int* abort_flag, const float* ref_ring, const float* inv_in,
                                           int row, int n_blocks, int q_row0, int b, int h) {
   const uint32_t lane_base = static_cast<uint32_t>(row & ~31) << 16;
-  const uint32_t t_t = tmem_base + lane_base + 256;
-  const uint32_t t_o = tmem_base + lane_base + 384;
-  constexpr int kUnits = D / 64;          // 64-channel units per block
+  const uint32_t t_src = tmem_base + lane_base + 384;
+  float o[D];                  // this row of the fp32 output, relative to 2^r_out
+#pragma unroll
+  for (int i = 0; i < D; ++i) o[i] = 0.0f;
   float r_out = -INFINITY;     // reference exponent O is expressed against
   bool ok = true;
 #ifdef SAGE_TRACE
@@ -276,65 +297,45 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
 #endif
 #pragma unroll 1
   for (int j = 0; j < n_blocks; ++j) {
-    float alpha = 1.0f, beta = 1.0f;
-    bool plain = false;
-#pragma unroll 1
-    for (int half = 0; half < kUnits; ++half) {
-      const int u = j * kUnits + half;
-      const int slot = u & 1;
-      ok = wait_bar_warp(bars + 8 * (kBarTFull + slot), (u >> 1) & 1, abort_flag, 30);
-      if (!ok) break;
-      ptx::tc_fence_after();
-#ifdef SAGE_TRACE
-      { const long long tn_ = clock64(); facc[0] += tn_ - fprev; fprev = tn_; }
-#endif
-      if (half == 0) {
-        const float r_blk = ref_ring[(j % kRefRing) * kTileQ + row];
-        const float r_new = fmaxf(r_out, r_blk);
-        // exact powers of two (the references are integers), and at most one of them differs from 1;
-        // an O that holds nothing yet is multiplied by 0
-        alpha = (r_out == r_new) ? 1.0f : pow2_int(fmaxf(r_out - r_new, -127.0f));
-        beta = (r_blk == r_new) ? 1.0f : pow2_int(fmaxf(r_blk - r_new, -127.0f));
-        r_out = r_new;
-        plain = (j > 0) && !__any_sync(0xffffffffu, alpha != 1.0f || beta != 1.0f);
-      }
-      const uint32_t t_src = t_t + slot * 64;
-      const uint32_t t_dst = t_o + half * 64;
-      if (plain) {
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) {
-          uint32_t t16[16], o[16];
-          ptx::tmem_ld16<0>(t_src + c0, t16);
-          ptx::tmem_ld16<0>(t_dst + c0, o);
-          ptx::tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(ptx::add_f32_f16lo(__uint_as_float(o[i]), t16[i]));
-          ptx::tmem_st16<0>(t_dst + c0, o);
-        }
-      } else {
-        const uint32_t beta16 = __half_as_ushort(__float2half_rn(beta));     // exact, or 0 below 2^-24
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) {
-          uint32_t t16[16], o[16];
-          ptx::tmem_ld16<0>(t_src + c0, t16);
-          if (j > 0) ptx::tmem_ld16<0>(t_dst + c0, o);
-          ptx::tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float acc = (j > 0) ? __uint_as_float(o[i]) * alpha : 0.0f;
-            o[i] = __float_as_uint(ptx::fma_f32_f16lo(t16[i], beta16, acc));
-          }
-          ptx::tmem_st16<0>(t_dst + c0, o);
-        }
-      }
-      ptx::tmem_wait_st();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bars + 8 * (kBarTFree + slot));
-#ifdef SAGE_TRACE
-      { const long long tn_ = clock64(); facc[1] += tn_ - fprev; fprev = tn_; facc[2] += (plain && half == 0) ? 1 : 0; }
-#endif
-    }
+    ok = wait_bar_warp(bars + 8 * kBarTFull, j & 1, abort_flag, 30);
     if (!ok) break;
+    ptx::tc_fence_after();
+#ifdef SAGE_TRACE
+    { const long long tn_ = clock64(); facc[0] += tn_ - fprev; fprev = tn_; }
+#endif
+    const float r_blk = ref_ring[(j % kRefRing) * kTileQ + row];
+    const float r_new = fmaxf(r_out, r_blk);
+    // exact powers of two (the references are integers), and at most one of them differs from 1;
+    // an O that holds nothing yet is multiplied by 0
+    const float alpha = (r_out == r_new) ? 1.0f : pow2_int(fmaxf(r_out - r_new, -127.0f));
+    const float beta = (r_blk == r_new) ? 1.0f : pow2_int(fmaxf(r_blk - r_new, -127.0f));
+    r_out = r_new;
+    const bool plain = !__any_sync(0xffffffffu, alpha != 1.0f || beta != 1.0f);
+    if (plain) {
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t t16[32];
+        ptx::tmem_ld32<0>(t_src + c0, t16);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::add_f32_f16lo(o[c0 + i], t16[i]);
+      }
+    } else {
+      const uint32_t beta16 = __half_as_ushort(__float2half_rn(beta));     // exact, or 0 below 2^-24
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t t16[32];
+        ptx::tmem_ld32<0>(t_src + c0, t16);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::fma_f32_f16lo(t16[i], beta16, o[c0 + i] * alpha);
+      }
+    }
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(bars + 8 * kBarTFree);
+#ifdef SAGE_TRACE
+    { const long long tn_ = clock64(); facc[1] += tn_ - fprev; fprev = tn_; facc[2] += plain ? 1 : 0; }
+#endif
   }
 #ifdef SAGE_TRACE
   if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && row == 0) {
@@ -347,21 +348,14 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
   if (ok && n_blocks > 0) {
     const int q_row = q_row0 + row;
     const float inv = inv_in[row];
-    const bool store = q_row < p.len_q;
-    unsigned short* orow = static_cast<unsigned short*>(p.out) + b * p.os_b + h * p.os_h + q_row * p.os_n;
+    if (q_row < p.len_q) {
+      unsigned short* orow = static_cast<unsigned short*>(p.out) + b * p.os_b + h * p.os_h + q_row * p.os_n;
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 16) {
-      uint32_t o[16];
-      ptx::tmem_ld16<0>(t_o + c0, o);
-      ptx::tmem_wait_ld();
-      uint32_t w[8];
+      for (int c0 = 0; c0 < D; c0 += 8) {
+        uint32_t w[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        w[i] = pack_out<OUT_DTYPE>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
-      if (store) {
-#pragma unroll
-        for (int i = 0; i < 8; i += 4)
-          *reinterpret_cast<uint4*>(orow + c0 + 2 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+        for (int i = 0; i < 4; ++i) w[i] = pack_out<OUT_DTYPE>(o[c0 + 2 * i] * inv, o[c0 + 2 * i + 1] * inv);
+        *reinterpret_cast<uint4*>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   }
@@ -396,6 +390,17 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   // another CTA of this launch already gave up: do not queue more bounded waits behind it
   if (launch_aborted(p)) return;
+#ifdef SAGE_TRACE
+  // debug builds: clock and wall time of the first and the last CTA of the grid, to separate the SM
+  // clock from per-CTA overheads
+  const bool tr_cta = (blockIdx.y == 0 && blockIdx.z == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1));
+  if (p.trace != nullptr && tr_cta && threadIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    p.trace[96 + (blockIdx.x == 0 ? 0 : 4)] = clock64();
+    p.trace[97 + (blockIdx.x == 0 ? 0 : 4)] = static_cast<long long>(gt);
+  }
+#endif
 
   const int kv_end = p.causal ? min(p.len_kv, q0 + kTileQ) : p.len_kv;
   const int n_blk = (kv_end + kBlockKV - 1) / kBlockKV;
@@ -410,15 +415,13 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       ptx::mbar_init(bars + 8 * (kBarVFull + s), 1);
       ptx::mbar_init(bars + 8 * (kBarVEmpty + s), 1);
     }
-    for (int t = 0; t < 2; ++t) {
+    for (int t = 0; t < 3; ++t) {
       ptx::mbar_init(bars + 8 * (kBarSFull + t), 1);
       ptx::mbar_init(bars + 8 * (kBarPFull + t), kTileQ);
     }
     ptx::mbar_init(bars + 8 * kBarSum, 2 * kTileQ);
-    for (int t = 0; t < 2; ++t) {
-      ptx::mbar_init(bars + 8 * (kBarTFull + t), 1);
-      ptx::mbar_init(bars + 8 * (kBarTFree + t), kTileQ);
-    }
+    ptx::mbar_init(bars + 8 * kBarTFull, 1);
+    ptx::mbar_init(bars + 8 * kBarTFree, kTileQ);
     ptx::mbar_init(bars + 8 * kBarStats, kTileQ);
     ptx::mbar_init(bars + 8 * kBarDrain, 1);
     *abort_flag = 0;
@@ -439,7 +442,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     softmax_role<D>(p, bars, tmem_base, abort_flag, ref_ring, inv_buf, ref_pub, sum_xchg, k_scales, warp >> 2,
                     threadIdx.x & 127, n_blk, q0, b, h);
   } else if (warp < 12) {
-    ptx::reg_dec<kRegsFold>();
+    ptx::reg_inc<kRegsFold>();
     fold_role<D, OUT_DTYPE>(p, bars, tmem_base, abort_flag, ref_ring, inv_buf, threadIdx.x - 256, n_blk, q0, b, h);
   } else {
     ptx::reg_dec<kRegsIssue>();
@@ -512,42 +515,41 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       constexpr int kRowBytesQK = (D == 64) ? 64 : 128;
       constexpr int kStepsQK = kRowBytesQK / 32;              // int8: 32 bytes of K per instruction
       const uint32_t idq = idesc_qk();
-      const uint32_t idp = idesc_pv<64, true>();              // fp16 accumulator, 64 channels per unit
+      const uint32_t idp = idesc_pv<D, true>();               // fp16 accumulator
       const uint64_t q_desc0 = desc_kmajor<kRowBytesQK>(smem_base + Plan::kQOff);
       const uint64_t k_desc0 = desc_kmajor<kRowBytesQK>(smem_base + Plan::kKOff);
       const uint64_t v_desc0 = desc_mnmajor(smem_base + Plan::kVOff, kBlockKV * 128);
 
-      // S[blk & 1] = Q . K(blk)^T
+      // S[blk % 3] = Q . K(blk)^T
       auto issue_qk = [&](int blk) {
-        const uint32_t d_t = tmem_base + (blk & 1) * 128;
+        const uint32_t d_t = tmem_base + (blk % 3) * 128;
         const uint64_t db0 = k_desc0 + static_cast<uint64_t>(((blk % kKStages) * Plan::kKBytes) >> 4);
         if (ptx::elect_one()) {
 #pragma unroll
           for (int s = 0; s < kStepsQK; ++s)
             ptx::mma_i8_ss(d_t, q_desc0 + static_cast<uint64_t>(s * 2), db0 + static_cast<uint64_t>(s * 2), idq, s != 0);
-          ptx::tc_commit(bars + 8 * (kBarSFull + (blk & 1)));
+          ptx::tc_commit(bars + 8 * (kBarSFull + (blk % 3)));
           ptx::tc_commit(bars + 8 * (kBarKEmpty + (blk % kKStages)));
         }
         __syncwarp();
       };
-      // T[slot] = P(blk) . V(blk)[:, 64 channels of unit `half`], fp16 accumulate from zero
-      constexpr int kUnits = D / 64;
-      auto issue_pv_unit = [&](int blk, int half, int slot, bool last) {
-        const uint32_t d_t = tmem_base + 256 + slot * 64;
-        const uint32_t a_t = tmem_base + (blk & 1) * 128;
-        const uint64_t db0 = v_desc0 + static_cast<uint64_t>(((blk % kVStages) * Plan::kVBytes + half * (kBlockKV * 128)) >> 4);
+      // T = P(blk) . V(blk), fp16 accumulate from zero
+      auto issue_pv = [&](int blk) {
+        const uint32_t d_t = tmem_base + 384;
+        const uint32_t a_t = tmem_base + (blk % 3) * 128;
+        const uint64_t db0 = v_desc0 + static_cast<uint64_t>(((blk % kVStages) * Plan::kVBytes) >> 4);
         if (ptx::elect_one()) {
 #pragma unroll
           for (int s = 0; s < kBlockKV / 16; ++s)
             ptx::mma_f16_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 2048) >> 4), idp, s != 0 ? 1u : 0u);
-          ptx::tc_commit(bars + 8 * (kBarTFull + slot));
-          if (last) ptx::tc_commit(bars + 8 * (kBarVEmpty + (blk % kVStages)));
+          ptx::tc_commit(bars + 8 * kBarTFull);
+          ptx::tc_commit(bars + 8 * (kBarVEmpty + (blk % kVStages)));
         }
         __syncwarp();
       };
 
       bool ok = wait_bar_warp(bars + 8 * kBarQFull, 0, abort_flag, 60);
-      for (int blk = 0; blk < 2 && blk < n_blk && ok; ++blk) {
+      for (int blk = 0; blk < 3 && blk < n_blk && ok; ++blk) {
         ok = wait_bar_warp(bars + 8 * (kBarKFull + blk % kKStages), 0, abort_flag, 61);
         if (!ok) break;
         ptx::tc_fence_after();
@@ -566,24 +568,19 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         ok = wait_bar_warp(bars + 8 * (kBarVFull + j % kVStages), (j / kVStages) & 1, abort_flag, 62);
         if (!ok) break;
         V4_MPH(1);
-        ok = wait_bar_warp(bars + 8 * (kBarPFull + (j & 1)), (j >> 1) & 1, abort_flag, 64);
+        ok = wait_bar_warp(bars + 8 * (kBarPFull + j % 3), (j / 3) & 1, abort_flag, 64);
         if (!ok) break;
         V4_MPH(2);
         ptx::tc_fence_after();
         V4_MPH(3);
-#pragma unroll 1
-        for (int half = 0; half < kUnits && ok; ++half) {
-          const int u = j * kUnits + half;
-          if (u >= 2) {                              // the unit that used this slot has been folded
-            ok = wait_bar_warp(bars + 8 * (kBarTFree + (u & 1)), ((u >> 1) - 1) & 1, abort_flag, 66);
-            if (!ok) break;
-            ptx::tc_fence_after();
-          }
-          issue_pv_unit(j, half, u & 1, half == kUnits - 1);
+        if (j >= 1) {                                // the previous block's T has been folded
+          ok = wait_bar_warp(bars + 8 * kBarTFree, (j - 1) & 1, abort_flag, 66);
+          if (!ok) break;
+          ptx::tc_fence_after();
         }
-        if (!ok) break;
+        issue_pv(j);
         V4_MPH(4);
-        const int nxt = j + 2;                      // reuses the score buffer P(j) was read from
+        const int nxt = j + 3;                      // reuses the score buffer P(j) was read from
         if (nxt < n_blk) {
           ok = wait_bar_warp(bars + 8 * (kBarKFull + nxt % kKStages), (nxt / kKStages) & 1, abort_flag, 63);
           if (!ok) break;
@@ -606,6 +603,14 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   if (warp == 12) ptx::tmem_dealloc(tmem_base, 512);
+#ifdef SAGE_TRACE
+  if (p.trace != nullptr && tr_cta && threadIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    p.trace[98 + (blockIdx.x == 0 ? 0 : 4)] = clock64();
+    p.trace[99 + (blockIdx.x == 0 ? 0 : 4)] = static_cast<long long>(gt);
+  }
+#endif
   if (threadIdx.x == 0 && *abort_flag != 0) publish_abort(p, *abort_flag);
 }
 
