@@ -142,17 +142,20 @@ def test_quant_idempotent_properties_at_full_size():
     assert int(q8.abs().max()) == 127
 
 
-@pytest.mark.parametrize("B,H,layout", [(1, 6, "HND"), (1, 5, "NHD"), (3, 2, "HND"), (3, 2, "NHD")])
-def test_smooth_quant_k_slicing_does_not_change_results(B, H, layout, monkeypatch):
+@pytest.mark.parametrize("B,H,N,layout", [(1, 6, 700, "HND"), (1, 5, 700, "NHD"), (3, 2, 700, "HND"), (3, 2, 700, "NHD"),
+                                          (1, 40, 4096, "HND"), (5, 8, 4096, "NHD")])
+def test_smooth_quant_k_slicing_does_not_change_results(B, H, N, layout, monkeypatch):
     """K mean + quantisation processed in L2-sized slices (of heads, or of batches) gives exactly the
     mean and the int8 values / scales of the unsliced two-step path."""
     from sageattention import _capi as C
     from sageattention import quant
     cuda_or_fail()
-    _, k, _ = make_qkv(B, H, H, 700, 128, torch.bfloat16, layout, seed=B * 10 + H, k_bias=2.0)
+    # (the long cases have enough planes that a slice on its own would split its rows differently
+    # from the whole tensor: the row split must follow the whole tensor)
+    _, k, _ = make_qkv(B, H, H, N, 128, torch.bfloat16, layout, seed=B * 10 + H, k_bias=2.0)
     km_ref = quant.mean_k(k, layout)
     k8_ref, ks_ref = quant._quant_one(k, km_ref, 64, 64, C.GROUP_K_THREAD, layout, "full")
-    for slice_bytes in (1, 2 * 700 * 128 * 2, 64 << 20):
+    for slice_bytes in (0, 1, 2 * N * 128 * 2, 8 * N * 128 * 2, 64 << 20):
         monkeypatch.setattr(quant, "_L2_SLICE_BYTES", slice_bytes)
         km, k8, ks = quant.smooth_quant_k(k, 64, 64, C.GROUP_K_THREAD, layout, "full")
         torch.cuda.synchronize()
