@@ -141,6 +141,16 @@ int sage_b200_cast_v_f16(const void* v, void* out, int dtype, int batch, int hea
                          void* stream);
 
 /*
+ * V smoothing for the fp16 accumulator: out = fp16(v - v_mean), the difference rounded to V's dtype
+ * first, as `(v - vm.unsqueeze(seq)).to(torch.float16)` does (sageattention/cuda_attn.py:209-211).
+ * `v_mean` is the channel mean over the sequence, (batch, heads, head_dim) contiguous in V's dtype:
+ * `v.mean(dim=seq)`, which sage_b200_mean_k computes for any (batch, heads, len, head_dim) tensor.
+ */
+int sage_b200_smooth_v_f16(const void* v, const void* v_mean, void* out, int dtype, int batch, int heads,
+                           int len, int head_dim, const int64_t v_strides[3], const int64_t out_strides[3],
+                           void* stream);
+
+/*
  * Attention core on quantised Q/K and fp16 V.
  * Replaces torch.ops.sageattention_qattn_sm80.qk_int8_sv_f16_accum_f32_attn,
  * ..._accum_f16_attn and ..._accum_f16_attn_inst_buf (csrc/qattn/pybind_sm80.cpp:24-98,
@@ -161,6 +171,21 @@ int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* ou
                        const int64_t v_strides[3], const int64_t o_strides[3], int is_causal,
                        float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k,
                        int granularity, int pv_accum, void* stream);
+
+/*
+ * The same with fp16 accumulation of a smoothed V and the channel mean added back to the normalised
+ * output, in the output type.  Replaces `qk_int8_sv_f16_accum_f16_fuse_v_mean_attn`
+ * (csrc/qattn/pybind_sm80.cpp:73-89, kernel csrc/qattn/qk_int8_sv_f16_kernel_sm80.cuh:551-569).
+ *   v       the smoothed V (sage_b200_smooth_v_f16), fp16
+ *   v_mean  (batch, heads_kv, head_dim) contiguous, in the OUTPUT dtype, 16-byte aligned
+ */
+int sage_b200_attn_fwd_fuse_v_mean(const int8_t* q, const int8_t* k, const void* v, const void* v_mean,
+                                   void* out, const float* q_scale, const float* k_scale, float* lse,
+                                   int32_t* status, int out_dtype, int batch, int heads_q, int heads_kv,
+                                   int len_q, int len_kv, int head_dim, const int64_t q_strides[3],
+                                   const int64_t k_strides[3], const int64_t v_strides[3],
+                                   const int64_t o_strides[3], int is_causal, float sm_scale, int blk_q,
+                                   int blk_k, int warp_q, int warp_k, int granularity, void* stream);
 
 /*
  * V in fp8 e4m3 with one fp32 scale per (batch, head, channel): scale = max|v| over the sequence / 448,

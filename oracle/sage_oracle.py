@@ -179,14 +179,16 @@ def expand_k_scale(k_scale: torch.Tensor, nk: int, BLKK: int, WARPK: int, granul
 def attend(q_int8, k_int8, v16, q_scale, k_scale, tensor_layout="HND", is_causal=False,
            sm_scale=None, pv_accum_dtype="fp32", granularity="per_thread",
            BLKQ=128, WARPQ=32, BLKK=64, WARPK=64, out_dtype=torch.float16,
-           return_lse=False, p_dtype=torch.float16, p_gain=1.0, sum_rounded=True):
+           return_lse=False, p_dtype=torch.float16, p_gain=1.0, sum_rounded=True, v_mean=None):
     """Flash-style forward on pre-quantised Q/K, in the reference's operation order:
     per BLKK-key block  S -> scale -> running max (base 2) -> P = 2^(S*a - m) -> P16 ->
     d += rowsum(P16) -> O = O*alpha + P16 @ V16, then O * (1/d).  ``pv_accum_dtype``:
     "fp32" keeps O in fp32; "fp16+fp32" rounds each block's P16@V16 to fp16 before the
     fp32 add (attn_utils.cuh:447-518); "fp16" keeps O itself in fp16 and rescales it
     with alpha rounded to fp16 (attn_utils.cuh:313-336).  Returns O in the input layout
-    (and the base-2 LSE = log2(d) + m as (B,Hq,Nq) when asked)."""
+    (and the base-2 LSE = log2(d) + m as (B,Hq,Nq) when asked).  ``v_mean`` ((B,Hkv,D), fp16
+    accumulate only): the channel mean of a smoothed V, added to the output after its rounding to
+    the output type (qk_int8_sv_f16_kernel_sm80.cuh:551-569)."""
     q8 = to_bhnd(q_int8, tensor_layout).float()
     k8 = to_bhnd(k_int8, tensor_layout).float()
     v = to_bhnd(v16, tensor_layout).float()
@@ -243,10 +245,29 @@ def attend(q_int8, k_int8, v16, q_scale, k_scale, tensor_layout="HND", is_causal
             m = m_new
         o[:, :, q0:q1] = acc.float() / d[..., None]
         lse[:, :, q0:q1] = torch.log2(d) + m
-    out = from_bhnd(o.to(out_dtype), tensor_layout).contiguous()
+    if pv_accum_dtype == "fp16":
+        o = o.half().float()                 # normalize_d leaves a half accumulator (attn_utils.cuh:565-567)
+    o = o.to(out_dtype)
+    if v_mean is not None:
+        if pv_accum_dtype != "fp16":
+            raise ValueError("v_mean goes with pv_accum_dtype='fp16' only.")
+        vm = v_mean.to(out_dtype)
+        if grp > 1:
+            vm = vm.repeat_interleave(grp, dim=1)
+        o = (o.float() + vm[:, :, None, :].float()).to(out_dtype)      # __hadd2 in the output type
+    out = from_bhnd(o, tensor_layout).contiguous()
     if return_lse:
         return out, lse
     return out
+
+
+def smooth_v(v, tensor_layout="HND"):
+    """(smoothed_v fp16, vm): vm = v.mean over the sequence in v's dtype, smoothed = (v - vm) in
+    v's dtype, then .to(float16) (cuda_attn.py:209-211)."""
+    seq_dim = 2 if tensor_layout == "HND" else 1
+    vm = v.float().mean(dim=seq_dim).to(v.dtype)
+    sm = (v - vm.unsqueeze(seq_dim)).to(torch.float16)
+    return sm, vm
 
 
 def quant_v_fp8(v, tensor_layout="HND"):
@@ -286,7 +307,7 @@ def lse_correction(q, km, tensor_layout):
 
 def sageattn(q, k, v, tensor_layout="HND", is_causal=False, pv_accum_dtype="fp32",
              smooth_k=True, return_lse=False, sm_scale=None, granularity="per_thread",
-             qk_config=(128, 64, 32, 64)):
+             qk_config=(128, 64, 32, 64), smooth_v=False):
     """The whole front end (cuda_attn.py:126-274) on CPU tensors: pad D, K mean, quantise,
     attend, slice, LSE fix-up."""
     head_dim = q.size(-1)
@@ -302,8 +323,11 @@ def sageattn(q, k, v, tensor_layout="HND", is_causal=False, pv_accum_dtype="fp32
         q8, qs, k8, ks = quant_per_thread(q, k, km, blk_q, warp_q, blk_k, warp_k, tensor_layout)
     else:
         q8, qs, k8, ks = quant_per_block(q, k, km, blk_q, blk_k, tensor_layout)
-    res = attend(q8, k8, v.to(torch.float16), qs, ks, tensor_layout, is_causal, sm_scale,
-                 pv_accum_dtype, granularity, blk_q, warp_q, blk_k, warp_k, q.dtype, return_lse)
+    v16, vm = v.to(torch.float16), None
+    if smooth_v and pv_accum_dtype == "fp16":
+        v16, vm = globals()["smooth_v"](v, tensor_layout)
+    res = attend(q8, k8, v16, qs, ks, tensor_layout, is_causal, sm_scale,
+                 pv_accum_dtype, granularity, blk_q, warp_q, blk_k, warp_k, q.dtype, return_lse, v_mean=vm)
     if not return_lse:
         return res[..., :head_dim]
     out, lse = res

@@ -24,6 +24,7 @@ struct AttnParams {
   const float* q_scale;
   const float* k_scale;
   const float* v_scale;          // fp8 P.V only: (batch, heads_kv, head_dim)
+  const unsigned short* v_mean;  // fp16 accumulate with a smoothed V only: (batch, heads_kv, head_dim), output dtype
   void* out;
   float* lse;
   int32_t* status;
@@ -75,6 +76,19 @@ __device__ __forceinline__ void publish_abort(const AttnParams& p, int code) {
 #else
 #define SAGE_TR(role, ev, j) do {} while (0)
 #endif
+
+// packed add of two values of the output type (reference: __hadd2 on DTypeOut2,
+// csrc/qattn/qk_int8_sv_f16_kernel_sm80.cuh:551-569)
+template <int OUT_DTYPE>
+__device__ __forceinline__ uint32_t add2_out(uint32_t a, uint32_t b) {
+  if constexpr (OUT_DTYPE == SAGE_B200_BF16) {
+    const __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  } else {
+    const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+}
 
 // Bounded mbarrier wait.  Returns false if the CTA is aborting.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {

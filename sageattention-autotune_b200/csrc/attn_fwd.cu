@@ -134,7 +134,7 @@ static long long* g_trace = nullptr;
 extern "C" void sage_b200_set_trace(long long* ptr) { g_trace = ptr; }
 #endif
 
-static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const float* v_scale, void* out,
+static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const float* v_scale, const void* v_mean, void* out,
                                   const float* q_scale, const float* k_scale, float* lse, int32_t* status,
                                   int out_dtype, int batch, int heads_q, int heads_kv, int len_q, int len_kv,
                                   int head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
@@ -154,6 +154,8 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   SAGE_REQUIRE((pv_accum == SAGE_B200_PV_F8) == (v_scale != nullptr),
                "attn_fwd: the fp8 mode (and only it) takes a v_scale; use sage_b200_attn_fwd_fp8");
   SAGE_REQUIRE(v_scale == nullptr || aligned16(v_scale), "attn_fwd: v_scale must be 16-byte aligned");
+  SAGE_REQUIRE(v_mean == nullptr || (pv_accum == SAGE_B200_PV_F16 && aligned16(v_mean)),
+               "attn_fwd: a V mean goes with fp16 accumulation only and must be 16-byte aligned");
   SAGE_REQUIRE(granularity != SAGE_B200_GRAN_PER_THREAD || aligned16(k_scale),
                "attn_fwd: per-thread k_scale must be 16-byte aligned (it is read four groups at a time)");
   if (head_dim != 64 && head_dim != 128) {
@@ -176,6 +178,7 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   p.q_scale = q_scale;
   p.k_scale = k_scale;
   p.v_scale = v_scale;
+  p.v_mean = static_cast<const unsigned short*>(v_mean);
   p.out = out;
   p.lse = lse;
   p.status = status;
@@ -233,9 +236,22 @@ extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* 
                                   int granularity, int pv_accum, void* stream) {
   if (pv_accum == SAGE_B200_PV_F8)
     return fail(SAGE_B200_ERR_INVALID, "attn_fwd: the fp8 mode needs a v_scale; use sage_b200_attn_fwd_fp8");
-  return attn_fwd_impl(q, k, v, nullptr, out, q_scale, k_scale, lse, status, out_dtype, batch, heads_q, heads_kv,
+  return attn_fwd_impl(q, k, v, nullptr, nullptr, out, q_scale, k_scale, lse, status, out_dtype, batch, heads_q, heads_kv,
                        len_q, len_kv, head_dim, q_strides, k_strides, v_strides, o_strides, is_causal, sm_scale,
                        blk_q, blk_k, warp_q, warp_k, granularity, pv_accum, stream);
+}
+
+extern "C" int sage_b200_attn_fwd_fuse_v_mean(const int8_t* q, const int8_t* k, const void* v, const void* v_mean,
+                                              void* out, const float* q_scale, const float* k_scale, float* lse,
+                                              int32_t* status, int out_dtype, int batch, int heads_q, int heads_kv,
+                                              int len_q, int len_kv, int head_dim, const int64_t q_strides[3],
+                                              const int64_t k_strides[3], const int64_t v_strides[3],
+                                              const int64_t o_strides[3], int is_causal, float sm_scale, int blk_q,
+                                              int blk_k, int warp_q, int warp_k, int granularity, void* stream) {
+  SAGE_REQUIRE(v_mean != nullptr, "attn_fwd_fuse_v_mean: null v_mean");
+  return attn_fwd_impl(q, k, v, nullptr, v_mean, out, q_scale, k_scale, lse, status, out_dtype, batch, heads_q,
+                       heads_kv, len_q, len_kv, head_dim, q_strides, k_strides, v_strides, o_strides, is_causal,
+                       sm_scale, blk_q, blk_k, warp_q, warp_k, granularity, SAGE_B200_PV_F16, stream);
 }
 
 extern "C" int sage_b200_attn_fwd_fp8(const int8_t* q, const int8_t* k, const void* v, const float* v_scale,
@@ -246,7 +262,7 @@ extern "C" int sage_b200_attn_fwd_fp8(const int8_t* q, const int8_t* k, const vo
                                       const int64_t o_strides[3], int is_causal, float sm_scale, int blk_q,
                                       int blk_k, int warp_q, int warp_k, int granularity, void* stream) {
   SAGE_REQUIRE(v_scale != nullptr, "attn_fwd_fp8: null v_scale");
-  return attn_fwd_impl(q, k, v, v_scale, out, q_scale, k_scale, lse, status, out_dtype, batch, heads_q, heads_kv,
+  return attn_fwd_impl(q, k, v, v_scale, nullptr, out, q_scale, k_scale, lse, status, out_dtype, batch, heads_q, heads_kv,
                        len_q, len_kv, head_dim, q_strides, k_strides, v_strides, o_strides, is_causal, sm_scale,
                        blk_q, blk_k, warp_q, warp_k, granularity, SAGE_B200_PV_F8, stream);
 }

@@ -377,6 +377,18 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
           const float hi = __half2float(__ushort_as_half(static_cast<unsigned short>(o[2 * i + 1] & 0xffffu)));
           w[i] = pack_out<OUT_DTYPE>(__half2float(__float2half_rn(lo * inv)), __half2float(__float2half_rn(hi * inv)));
         }
+        if (p.v_mean != nullptr) {
+          // V was smoothed by its channel mean: add the mean back, in the output type
+          const uint4* vm = reinterpret_cast<const uint4*>(p.v_mean + (static_cast<int64_t>(b) * p.heads_kv + h_kv) * D + c0);
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            const uint4 m4 = __ldg(vm + i / 4);
+            w[i] = add2_out<OUT_DTYPE>(w[i], m4.x);
+            w[i + 1] = add2_out<OUT_DTYPE>(w[i + 1], m4.y);
+            w[i + 2] = add2_out<OUT_DTYPE>(w[i + 2], m4.z);
+            w[i + 3] = add2_out<OUT_DTYPE>(w[i + 3], m4.w);
+          }
+        }
         if (store) {
 #pragma unroll
           for (int i = 0; i < 16; i += 4)

@@ -87,11 +87,16 @@ def _lse_correction(q, km, tensor_layout):
 
 
 def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_layout, is_causal, sm_scale,
-                       qk_config, pv_accum_dtype="fp32", return_lse=False, granularity="per_thread", v_scale=None):
+                       qk_config, pv_accum_dtype="fp32", return_lse=False, granularity="per_thread", v_scale=None,
+                       v_mean=None):
     """The attention core on pre-quantised tensors; the counterpart of
     torch.ops.sageattention_qattn_sm80.qk_int8_sv_f16_accum_*_attn (csrc/qattn/pybind_sm80.cpp:24-98).
-    Writes `output` in place and returns the base-2 LSE ((0,)-shaped when not requested)."""
+    Writes `output` in place and returns the base-2 LSE ((0,)-shaped when not requested).
+    `v_mean` ((batch, kv_heads, head_dim), output dtype) selects the fp16 accumulator with the mean of a
+    smoothed V added back (..._accum_f16_fuse_v_mean_attn)."""
     fp8 = v_scale is not None
+    if v_mean is not None and (fp8 or pv_accum_dtype != "fp16"):
+        raise ValueError("v_mean goes with pv_accum_dtype='fp16' only.")
     if not fp8 and pv_accum_dtype not in _PV_CODE:
         raise ValueError("pv_accum_dtype must be 'fp32', 'fp16', or 'fp16+fp32'.")
     b, hq, nq, d = C.bhnd(q_int8, tensor_layout)
@@ -106,6 +111,15 @@ def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_
         if fp8:
             C.check(C.lib().sage_b200_attn_fwd_fp8(
                 q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), v_scale.data_ptr(), output.data_ptr(),
+                q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
+                status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
+                C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
+                C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
+                1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran, C.stream_ptr(dev)))
+        elif v_mean is not None:
+            v_mean = v_mean.to(output.dtype).contiguous()
+            C.check(C.lib().sage_b200_attn_fwd_fuse_v_mean(
+                q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), v_mean.data_ptr(), output.data_ptr(),
                 q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
                 status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
                 C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
@@ -158,8 +172,8 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         if pv_accum_dtype in ("fp32", "fp16+fp32"):
             warnings.warn("pv_accum_dtype is fp32 or fp16+fp32, smooth_v will be ignored.", stacklevel=2)
             smooth_v = False
-        else:
-            raise NotImplementedError("smooth_v with pv_accum_dtype='fp16' is not built for sm_100a yet.")
+        elif pv_accum_dtype == _FP8_PV:
+            raise ValueError("smooth_v goes with pv_accum_dtype='fp16' only.")
 
     # TMA and the vector kernels need 16-byte aligned rows
     def _aligned(t):
@@ -181,16 +195,19 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
             km = None
             k_int8, k_scale = Q._quant_one(k, None, blk_k, k_warp, k_kind, tensor_layout, Q.default_div_mode())
     v_scale = None
+    v_mean = None
     with _Timed("cast_v"):
         if pv_accum_dtype == _FP8_PV:
             v_fp16, v_scale = Q.quant_v_fp8(v, tensor_layout)
+        elif smooth_v:
+            v_fp16, v_mean = Q.smooth_v_fp16(v, tensor_layout)
         else:
             v_fp16 = cast_v_fp16(v, tensor_layout)
 
     output = torch.empty(q.size(), dtype=dtype, device=q.device)
     with _Timed("attn"):
         lse = attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_layout, is_causal,
-                                 sm_scale, qk_config, pv_accum_dtype, return_lse, qk_quant_gran, v_scale)
+                                 sm_scale, qk_config, pv_accum_dtype, return_lse, qk_quant_gran, v_scale, v_mean)
     output = output[..., :head_dim]
     if not return_lse:
         return output

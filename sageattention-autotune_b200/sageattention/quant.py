@@ -143,6 +143,21 @@ def cast_v_fp16(v: torch.Tensor, tensor_layout: str = "HND") -> torch.Tensor:
     return out
 
 
+def smooth_v_fp16(v: torch.Tensor, tensor_layout: str = "HND"):
+    """(smoothed_v, vm): vm = v.mean over the sequence, (batch, heads, head_dim) in v's dtype, and
+    (v - vm).to(float16) with the difference rounded to v's dtype first (reference: cuda_attn.py:209-211)."""
+    _check_in(v, "v")
+    b, h, n, d = C.bhnd(v, tensor_layout)
+    vm4 = mean_k(v, tensor_layout)                      # the channel-mean kernels do not care which tensor it is
+    vm = vm4.view(b, h, d)
+    out = torch.empty(v.shape, dtype=torch.float16, device=v.device)
+    with torch.cuda.device(v.device):
+        C.check(C.lib().sage_b200_smooth_v_f16(
+            v.data_ptr(), vm.data_ptr(), out.data_ptr(), C.dtype_code(v.dtype), b, h, n, d,
+            C.bhn_strides(v, tensor_layout), C.bhn_strides(out, tensor_layout), C.stream_ptr(v.device)))
+    return out, vm
+
+
 def quant_v_fp8(v: torch.Tensor, tensor_layout: str = "HND"):
     """(v_fp8, v_scale): V in fp8 e4m3 with one fp32 scale per (batch, head, channel),
     scale = max|v| over the sequence / 448.  v_fp8 keeps v's shape and dimension order

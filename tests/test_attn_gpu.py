@@ -132,6 +132,71 @@ def test_core_matches_reference_cuda_kernel(case, mode, op):
     print(case, mode, c)
 
 
+@pytest.mark.parametrize("case", ["c2_like", "c3_like", "c4_like"])
+def test_fuse_v_mean_matches_reference_cuda_kernel(case):
+    """smooth_v: V minus its channel mean through the fp16 accumulator, the mean added back in the
+    epilogue.  The smoothed V and the mean (ours: bit-identical to the torch expressions of the
+    reference when fed the same mean) go into the reference's ..._fuse_v_mean_attn kernel and ours."""
+    from sageattention import quant
+    from sageattention.core import attn_fwd_quantized
+    cuda_or_fail()
+    ref = reference_ops()
+    assert ref is not None, "oracle/_ref/libsage_ref_sm80.so is missing: run make -C oracle"
+    if case == "c2_like":
+        args = dict(B=2, Hq=4, Hkv=4, N=1024, D=64, dtype=torch.float16, layout="HND", seed=11, k_bias=3.0)
+        causal = False
+    elif case == "c3_like":
+        args = dict(B=1, Hq=8, Hkv=2, N=2048, D=128, dtype=torch.bfloat16, layout="NHD", seed=12, k_outliers=20.0)
+        causal = True
+    else:
+        args = dict(B=1, Hq=2, Hkv=2, N=2320, D=128, dtype=torch.bfloat16, layout="HND", seed=13, k_bias=2.0)
+        causal = False
+    q, k, v = make_qkv(**args)
+    layout = args["layout"]
+    seq_dim = 2 if layout == "HND" else 1
+    v = v + 1.5 * torch.randn_like(v.select(seq_dim, 0)).unsqueeze(seq_dim)          # a channel offset worth removing
+    v_s, vm = quant.smooth_v_fp16(v, layout)
+    # the smoothing itself: exactly the reference's torch expression on the same mean, and the mean
+    # within one unit in the last place of torch's
+    assert torch.equal(v_s, (v - vm.unsqueeze(seq_dim)).to(torch.float16))
+    vm_t = v.mean(dim=seq_dim)
+    ulp = torch.exp2(torch.floor(torch.log2(vm_t.float().abs().clamp_min(1e-30))) - (10 if v.dtype == torch.float16 else 7))
+    assert bool(((vm.float() - vm_t.float()).abs() <= ulp).all())
+    km = quant.mean_k(k, layout)
+    q8, qs, k8, ks = quant.per_thread_int8(q, k, km, *[CFG[i] for i in (0, 2, 1, 3)], layout, div="ieee")
+    out = torch.empty_like(q)
+    attn_fwd_quantized(q8, k8, v_s, out, qs, ks, layout, causal, q.size(-1) ** -0.5, CFG, "fp16", False,
+                       "per_thread", None, vm)
+    ref_out = torch.empty_like(q)
+    ref.qk_int8_sv_f16_accum_f16_fuse_v_mean_attn(q8, k8, v_s, ref_out, qs, ks, vm, 0 if layout == "NHD" else 1, causal,
+                                                  q.size(-1) ** -0.5, *CFG, False)
+    torch.cuda.synchronize()
+    _assert_close(out, ref_out, ("fuse_v_mean", case))
+    exp = O.attend(q8.cpu(), k8.cpu(), v_s.cpu(), qs.cpu(), ks.cpu(), layout, causal, None, "fp16", "per_thread",
+                   128, 32, 64, 64, q.dtype, False, v_mean=vm.cpu())
+    _assert_close(out, exp, ("fuse_v_mean vs oracle", case))
+
+
+def test_sageattn_smooth_v_front_end():
+    """smooth_v=True through the public call: fp16 accumulate takes the smoothed path and stays within
+    the reference's acceptance bounds against exact attention even with a large V offset, where the
+    plain fp16 accumulator loses accuracy; the fp32 modes warn and ignore it as the reference does."""
+    import warnings
+    import sageattention
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 4, 4, 2048, 128, torch.float16, "HND", seed=21)
+    v = v + 8.0 * torch.randn(1, 4, 1, 128, device=v.device, dtype=v.dtype)
+    exp, _ = O.sdpa_fp32(q.cpu(), k.cpu(), v.cpu(), "HND", True)
+    out = sageattention.sageattn(q, k, v, is_causal=True, pv_accum_dtype="fp16", smooth_v=True)
+    c = O.compare(out.cpu(), exp)
+    assert c["fro_rel"] <= 0.02 and c["max_abs"] <= 0.1, c
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        out32 = sageattention.sageattn(q, k, v, is_causal=True, pv_accum_dtype="fp32", smooth_v=True)
+    assert any("smooth_v will be ignored" in str(x.message) for x in w)
+    assert torch.equal(out32, sageattention.sageattn(q, k, v, is_causal=True, pv_accum_dtype="fp32"))
+
+
 @pytest.mark.parametrize("layout", ["HND", "NHD"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("causal", [False, True])

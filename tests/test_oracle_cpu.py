@@ -76,6 +76,21 @@ def test_oracle_end_to_end_close_to_fp32_attention():
             assert float((lse - ref_lse).abs().max()) < 0.05
 
 
+def test_oracle_smooth_v_removes_the_channel_offset_from_the_fp16_accumulator():
+    """V with a large per-channel offset: the smoothed fp16 path (mean removed, added back after the
+    normalisation) must be at least as close to exact attention as the plain fp16 accumulator."""
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(1, 2, 384, 64, generator=g).bfloat16()
+    k = torch.randn(1, 2, 384, 64, generator=g).bfloat16()
+    v = (torch.randn(1, 2, 384, 64, generator=g) + 12.0 * torch.randn(1, 2, 1, 64, generator=g)).bfloat16()
+    ref, _ = O.sdpa_fp32(q, k, v, "HND", True)
+    plain = O.compare(O.sageattn(q, k, v, "HND", True, "fp16"), ref)
+    smooth = O.compare(O.sageattn(q, k, v, "HND", True, "fp16", smooth_v=True), ref)
+    assert smooth["fro_rel"] <= plain["fro_rel"] + 1e-4 and smooth["max_abs"] <= 0.13, (plain, smooth)
+    sm, vm = O.smooth_v(v, "HND")
+    assert sm.dtype == torch.float16 and vm.shape == (1, 2, 64) and vm.dtype == v.dtype
+
+
 def test_header_symbols_are_exported():
     hdr = open(os.path.join(ROOT, "include", "sage_b200.h")).read()
     declared = sorted(set(re.findall(r"\b(sage_b200_[a-z0-9_]+)\s*\(", hdr)))
