@@ -191,17 +191,28 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     }
     m_run = fmaxf(m_run, m_blk);
 
-    // choose the reference point and the factor by which earlier work must shrink
+    // Choose the reference point and the factor by which earlier work must shrink.  fp32 accumulators
+    // tolerate P up to 2^8 and move the reference lazily.  The fp16 accumulators and the e4m3 P need
+    // P <= 1; their reference is the running maximum rounded UP to an integer, which still bounds P by
+    // 1, moves only when the maximum crosses an integer (rarely after the first blocks, so the rescale
+    // of O is skipped for most blocks) and makes every rescale factor an exact power of two.
+    constexpr bool kExactRef = kF16Acc || kInstBuf || kFp8;
     float alpha = 1.0f;
     bool rescale = false;
     if (j == 0) {
-      m_used = m_run;
+      m_used = kExactRef ? ceilf(m_run) : m_run;
     } else {
       const float grow = m_run - m_used;
-      // (fp8: P must stay <= 1 so that 448*P fits e4m3, hence no lazy rescale)
-      if ((kF16Acc || kInstBuf || kFp8) ? (grow > 0.0f) : (grow > kLazyRescale)) {
-        alpha = ptx::ex2(m_used - m_run);
-        m_used = m_run;
+      if (kExactRef ? (grow > 0.0f) : (grow > kLazyRescale)) {
+        const float m_next = kExactRef ? ceilf(m_run) : m_run;
+        if constexpr (kExactRef) {
+          // 2^(m_used - m_next) for integer arguments, exactly; 0 below the normal range
+          const int e = static_cast<int>(fmaxf(m_used - m_next, -127.0f)) + 127;
+          alpha = __int_as_float(e << 23);
+        } else {
+          alpha = ptx::ex2(m_used - m_next);
+        }
+        m_used = m_next;
         rescale = true;
       }
     }

@@ -159,8 +159,8 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         raise ValueError("tensor_layout must be 'NHD' or 'HND'.")
     if pv_accum_dtype not in _PV_CODE and pv_accum_dtype != _FP8_PV:
         raise ValueError("pv_accum_dtype must be 'fp32', 'fp16', or 'fp16+fp32'.")
-    if qk_quant_gran not in ("per_thread", "per_block"):
-        raise ValueError("qk_quant_gran must be 'per_thread' or 'per_block'.")
+    if qk_quant_gran not in ("per_thread", "per_block", "per_warp"):
+        raise ValueError("qk_quant_gran must be 'per_thread', 'per_block' or 'per_warp'.")
 
     head_dim, q, k, v = _pad_qkv(q, k, v)
     if q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1:
@@ -181,6 +181,9 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
     q, k, v = _aligned(q), _aligned(k), _aligned(v)
 
     blk_q, blk_k, warp_q, warp_k = qk_config
+    if qk_quant_gran == "per_warp":
+        # one scale per WARPQ query rows and per BLKK keys: the per-block scheme with WARPQ-row Q blocks
+        blk_q, qk_config, qk_quant_gran = warp_q, (warp_q, blk_k, warp_q, blk_k), "per_block"
     per_thread = qk_quant_gran == "per_thread"
     with _Timed("quant_q"):
         q_int8, q_scale = Q._quant_one(q, None, blk_q, warp_q if per_thread else blk_q,

@@ -340,6 +340,26 @@ def test_sageattn_traces_under_torch_compile():
     assert got.shape == q.shape and torch.allclose(got.float(), exp.float(), atol=1e-3)
 
 
+@pytest.mark.parametrize("mode", ["fp32", "fp16+fp32"])
+def test_sageattn_per_warp_granularity(mode):
+    """qk_quant_gran="per_warp": one Q scale per WARPQ = 32 rows, one K scale per BLKK = 64 keys.  The
+    reference tree has no kernel of that name (parity unpinned); it is the per-block scheme with
+    32-row Q blocks, so the oracle's per-block quantiser and attention with BLKQ = 32 are the check."""
+    import sageattention
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 4, 2, 1100, 128, torch.float16, "HND", seed=41, k_bias=1.0)
+    out = sageattention.sageattn(q, k, v, is_causal=True, pv_accum_dtype=mode, qk_quant_gran="per_warp")
+    qc, kc, vc = q.cpu(), k.cpu(), v.cpu()
+    km = O.mean_k(kc, "HND")
+    q8, qs, k8, ks = O.quant_per_block(qc, kc, km, 32, 64, "HND")
+    assert qs.shape == (1, 4, -(-1100 // 32)) and ks.shape == (1, 2, -(-1100 // 64))
+    exp = O.attend(q8, k8, vc, qs, ks, "HND", True, None, mode, "per_block", 32, 32, 64, 64, torch.float16)
+    _assert_close(out, exp, ("per_warp", mode))
+    ref, _ = O.sdpa_fp32(qc, kc, vc, "HND", True)
+    c = O.compare(out.cpu(), ref)
+    assert c["fro_rel"] <= 0.02 and c["max_abs"] <= 0.1, c
+
+
 def test_sageattn_can_be_captured_in_a_cuda_graph(monkeypatch):
     """The whole call (quantisers, K mean, attention) allocates through torch's caching allocator and
     enqueues on the current stream only, so it can be captured once and replayed: the replay on new
