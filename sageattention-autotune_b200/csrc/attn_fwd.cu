@@ -61,8 +61,8 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   // "fp16+fp32" mode needs an fp16 partial product next to the scores and runs the one-tile kernel with
   // a fold warpgroup (attn_v4.cuh); SAGE_B200_KERNEL=coupled runs it on the two-tile kernel instead,
   // which folds inside the softmax warps (slower, kept as a cross-check).
-  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams);
-  int smem;
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams) = nullptr;
+  int smem = 0;
   int threads = kAttnThreads;
   int which = 0;               // index of the kernel in the per-device attribute cache below
   if constexpr (PV_MODE == SAGE_B200_PV_F16_F32) {
@@ -70,7 +70,12 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       const char* e = getenv("SAGE_B200_KERNEL");
       return e != nullptr && e[0] == 'c';
     }();
-    if (two_tile) {
+    if constexpr (D == 256) {
+      // 256 channels of fp16 partial product and of fp32 output do not fit the one-tile kernel's
+      // tensor memory and registers: the mode folds 64 channels at a time inside the softmax warps
+      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
+      smem = v1::SmemPlan<D>::kDynamic;
+    } else if (two_tile) {
       kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
       smem = v1::SmemPlan<D>::kDynamic;
     } else {
@@ -81,8 +86,12 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       which = 1;
     }
   } else if constexpr (PV_MODE == SAGE_B200_PV_F8) {
-    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
-    smem = v1::SmemPlan<D, true>::kDynamic;
+    if constexpr (D == 256) {
+      return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: the fp8 P.V mode is built for head_dim 64 and 128 only");
+    } else {
+      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
+      smem = v1::SmemPlan<D, true>::kDynamic;
+    }
   } else {
     kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
     smem = v1::SmemPlan<D>::kDynamic;
@@ -158,11 +167,10 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
                "attn_fwd: a V mean goes with fp16 accumulation only and must be 16-byte aligned");
   SAGE_REQUIRE(granularity != SAGE_B200_GRAN_PER_THREAD || aligned16(k_scale),
                "attn_fwd: per-thread k_scale must be 16-byte aligned (it is read four groups at a time)");
-  if (head_dim != 64 && head_dim != 128) {
-    if (head_dim == 256)
-      return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: head_dim 256 is not built yet");
-    return fail(SAGE_B200_ERR_INVALID, "attn_fwd: head_dim must be 64 or 128 (pad first), got %d", head_dim);
-  }
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256)
+    return fail(SAGE_B200_ERR_INVALID, "attn_fwd: head_dim must be 64, 128 or 256 (pad first), got %d", head_dim);
+  if (head_dim == 256 && pv_accum == SAGE_B200_PV_F8)
+    return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: the fp8 P.V mode is built for head_dim 64 and 128 only");
   SAGE_REQUIRE(blk_q == 32 || blk_q == 64 || blk_q == 128, "attn_fwd: blk_q must be 32, 64 or 128");
   if (blk_k != 64)
     return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: only blk_k = 64 scale blocks are built (got %d)", blk_k);
@@ -211,9 +219,10 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   constexpr int kStageRows = 128;   // keys per TMA stage in both kernels
   CUtensorMap mq, mk, mv;
   const CUtensorMapSwizzle swz_qk = (head_dim == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
-  int rc = make_map(&mq, q, 1, batch, heads_q, len_q, head_dim, q_strides, head_dim, kTileQ, swz_qk, "q");
+  const int box_qk = head_dim < 128 ? head_dim : 128;      // wider rows are staged as 128-byte panels
+  int rc = make_map(&mq, q, 1, batch, heads_q, len_q, head_dim, q_strides, box_qk, kTileQ, swz_qk, "q");
   if (rc) return rc;
-  rc = make_map(&mk, k, 1, batch, heads_kv, len_kv, head_dim, k_strides, head_dim, kStageRows, swz_qk, "k");
+  rc = make_map(&mk, k, 1, batch, heads_kv, len_kv, head_dim, k_strides, box_qk, kStageRows, swz_qk, "k");
   if (rc) return rc;
   if (pv_accum == SAGE_B200_PV_F8)
     rc = make_map(&mv, v, 1, batch, heads_kv, len_kv, head_dim, v_strides, head_dim, kStageRows, swz_qk, "v");
@@ -221,8 +230,10 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
     rc = make_map(&mv, v, 2, batch, heads_kv, len_kv, head_dim, v_strides, 64, kStageRows, CU_TENSOR_MAP_SWIZZLE_128B, "v");
   if (rc) return rc;
 
-  const dim3 grid((len_q + 2 * kTileQ - 1) / (2 * kTileQ), heads_q, batch);
+  const int rows_per_cta = (head_dim == 256 ? 1 : 2) * kTileQ;     // the one-tile kernel resets grid.x itself
+  const dim3 grid((len_q + rows_per_cta - 1) / rows_per_cta, heads_q, batch);
   if (head_dim == 64) return launch_attn_mode<64>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+  if (head_dim == 256) return launch_attn_mode<256>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
   return launch_attn_mode<128>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
 }
 

@@ -50,15 +50,20 @@ enum BarIdx {
   kNumBars = kBarDrain + 1
 };
 
+// head_dim 256 runs this kernel with ONE query tile per CTA (S + a 256-column O fill tensor memory
+// for one tile only) and two K/V stages instead of three (Q 32 KB + 2 x 32 KB + 2 x 64 KB = 224 KB).
 template <int D, bool F8 = false>
 struct SmemPlan {
+  static constexpr int kTiles = (D == 256) ? 1 : 2;
+  static constexpr int kStagesK = (D == 256) ? 2 : kKStages;
+  static constexpr int kStagesV = (D == 256) ? 2 : kVStages;
   static constexpr int kQBytes = kTileQ * D;                 // int8
   static constexpr int kKBytes = kBlockKV * D;               // int8
   static constexpr int kVBytes = kBlockKV * D * (F8 ? 1 : 2);  // fp16, or e4m3
   static constexpr int kQOff = 0;
-  static constexpr int kKOff = kQOff + 2 * kQBytes;
-  static constexpr int kVOff = kKOff + kKStages * kKBytes;
-  static constexpr int kBarOff = kVOff + kVStages * kVBytes;
+  static constexpr int kKOff = kQOff + kTiles * kQBytes;
+  static constexpr int kVOff = kKOff + kStagesK * kKBytes;
+  static constexpr int kBarOff = kVOff + kStagesV * kVBytes;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamic = kTotal + 1024;             // slack for manual 1024-byte alignment
@@ -465,8 +470,10 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int h = blockIdx.y;
   const int h_kv = h / (p.heads_q / p.heads_kv);
   // causal: the heaviest tiles (largest query index) go first
+  constexpr int kTiles = Plan::kTiles;
+  constexpr int kStK = Plan::kStagesK, kStV = Plan::kStagesV;
   const int pair = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
-  const int q0 = pair * 2 * kTileQ;
+  const int q0 = pair * kTiles * kTileQ;
 
   // another CTA of this launch already gave up: do not queue more bounded waits behind it
   if (launch_aborted(p)) return;
@@ -476,7 +483,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   for (int t = 0; t < 2; ++t) {
     const int r0 = q0 + t * kTileQ;
     int kv_end = p.causal ? min(p.len_kv, r0 + kTileQ) : p.len_kv;
-    n_blk[t] = (r0 < p.len_q) ? (kv_end + kBlockKV - 1) / kBlockKV : 0;
+    n_blk[t] = (t < kTiles && r0 < p.len_q) ? (kv_end + kBlockKV - 1) / kBlockKV : 0;
   }
   const int n_max = max(n_blk[0], n_blk[1]);
 
@@ -522,19 +529,28 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       ptx::prefetch_tensormap(&tm_k);
       ptx::prefetch_tensormap(&tm_v);
       const uint32_t q_smem = smem_base + Plan::kQOff;
-      ptx::mbar_arrive_expect_tx(bars + 8 * kBarQFull, 2 * Plan::kQBytes);
-      ptx::tma_load_4d(q_smem, &tm_q, bars + 8 * kBarQFull, 0, q0, h, b);
-      ptx::tma_load_4d(q_smem + Plan::kQBytes, &tm_q, bars + 8 * kBarQFull, 0, q0 + kTileQ, h, b);
+      // Q and K rows wider than one 128-byte swizzle span (head_dim 256) are staged as panels of 128 bytes
+      constexpr int kPanelBytesQK = (D == 64) ? 64 : 128;
+      constexpr int kPanelsQKLoad = D / kPanelBytesQK;
+      ptx::mbar_arrive_expect_tx(bars + 8 * kBarQFull, kTiles * Plan::kQBytes);
+#pragma unroll
+      for (int t = 0; t < kTiles; ++t)
+#pragma unroll
+        for (int pn = 0; pn < kPanelsQKLoad; ++pn)
+          ptx::tma_load_4d(q_smem + t * Plan::kQBytes + pn * (kTileQ * kPanelBytesQK), &tm_q, bars + 8 * kBarQFull,
+                           pn * kPanelBytesQK, q0 + t * kTileQ, h, b);
       bool ok = true;
 #pragma unroll 1
       for (int j = 0; j < n_max && ok; ++j) {
-        const int ks = j % kKStages, vs = j % kVStages;
-        ok = wait_bar(bars + 8 * (kBarKEmpty + ks), ((j / kKStages) & 1) ^ 1, abort_flag, 50);
+        const int ks = j % kStK, vs = j % kStV;
+        ok = wait_bar(bars + 8 * (kBarKEmpty + ks), ((j / kStK) & 1) ^ 1, abort_flag, 50);
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarKFull + ks), Plan::kKBytes);
-        ptx::tma_load_4d(smem_base + Plan::kKOff + ks * Plan::kKBytes, &tm_k, bars + 8 * (kBarKFull + ks), 0,
-                         j * kBlockKV, h_kv, b);
-        ok = wait_bar(bars + 8 * (kBarVEmpty + vs), ((j / kVStages) & 1) ^ 1, abort_flag, 51);
+#pragma unroll
+        for (int pn = 0; pn < kPanelsQKLoad; ++pn)
+          ptx::tma_load_4d(smem_base + Plan::kKOff + ks * Plan::kKBytes + pn * (kBlockKV * kPanelBytesQK), &tm_k,
+                           bars + 8 * (kBarKFull + ks), pn * kPanelBytesQK, j * kBlockKV, h_kv, b);
+        ok = wait_bar(bars + 8 * (kBarVEmpty + vs), ((j / kStV) & 1) ^ 1, abort_flag, 51);
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarVFull + vs), Plan::kVBytes);
 #pragma unroll
@@ -544,7 +560,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       if (!ok) {
         // leave no copy in flight behind us: wait (bounded by the hardware try_wait) for what was issued
-        for (int s = 0; s < kKStages; ++s)
+        for (int s = 0; s < kStK; ++s)
           for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 0) &&
                           !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 1); ++i) {}
       }
@@ -636,13 +652,13 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
 #pragma unroll 1
       for (int j = 0; j < n_max && ok; ++j) {
-        const int vs = j % kVStages;
+        const int vs = j % kStV;
         const int nxt = j + 1;
-        const int ks = nxt % kKStages;
-        ok = wait_bar_warp(bars + 8 * (kBarVFull + vs), (j / kVStages) & 1, abort_flag, 62);
+        const int ks = nxt % kStK;
+        ok = wait_bar_warp(bars + 8 * (kBarVFull + vs), (j / kStV) & 1, abort_flag, 62);
         if (!ok) break;
         if (nxt < n_max) {
-          ok = wait_bar_warp(bars + 8 * (kBarKFull + ks), (nxt / kKStages) & 1, abort_flag, 63);
+          ok = wait_bar_warp(bars + 8 * (kBarKFull + ks), (nxt / kStK) & 1, abort_flag, 63);
           if (!ok) break;
         }
         if constexpr (!kInstBuf) {

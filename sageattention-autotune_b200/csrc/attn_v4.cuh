@@ -24,8 +24,9 @@
 // is an exact power of two.  Each block's reference travels to the fold warps, which keep the output's
 // own reference (the largest seen so far) and apply alpha = 2^(r_O - r_new) to O and
 // beta = 2^(r_block - r_new) to T; when both are 1 for a whole warp the fold is a plain add.  To keep
-// that the common case a warpgroup also folds the other's last published reference into its own
-// (an unsynchronised read: any earlier value is equally valid).  The two row sums are combined at the end.
+// that the common case a warpgroup also folds the other's reference of three blocks earlier into its
+// own (the latest one that is certain to exist, so the result is reproducible bit for bit).  The two
+// row sums are combined at the end.
 // Because the warpgroups are out of phase, one's tensor-memory and barrier latencies hide behind the
 // other's exponentials.
 #pragma once
@@ -35,7 +36,7 @@
 namespace sage {
 namespace v4 {
 
-constexpr int kRefRing = 4;        // block references in flight between the softmax and the fold warps
+constexpr int kRefRing = 8;        // block references: read by the fold warps, and three blocks later by the other softmax warpgroup
 constexpr int kScaleRing = 8;      // K dequantisation scales staged by the producer, one slot per block
 constexpr int kThreads = 512;
 // setmaxnreg is a warpgroup-wide instruction: the four warps of a group must ask for the same count
@@ -173,15 +174,18 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     }
     V4_PH(2);
 
-    // new reference: integer, at least this block's maximum, never below anything already used or
-    // published by the other warpgroup (whatever value of it this read happens to see)
-    const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk)), ref_pub[(wg ^ 1) * kTileQ + row]);
+    // new reference: integer, at least this block's maximum, never below anything already used, and
+    // not below the other warpgroup's reference of block j-3.  That block's softmax finished before
+    // the scores of block j could be issued, so the value is always the same one: results do not depend
+    // on how the two warpgroups happen to interleave.
+    const float r_other = (j >= 3) ? ref_ring[((j - 3) % kRefRing) * kTileQ + row] : -INFINITY;
+    const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk)), r_other);
     // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
     const float m_ref = (r_new == -INFINITY) ? 0.0f : r_new;
     const float shrink = (ref == r_new) ? 1.0f : pow2_int(fmaxf(ref - m_ref, -127.0f));
     ref = r_new;
     ref_pub[wg * kTileQ + row] = r_new;
-    ref_ring[(j % kRefRing) * kTileQ + row] = r_new;      // (slot reuse: block j-4 was folded before S(j) existed)
+    ref_ring[(j % kRefRing) * kTileQ + row] = r_new;      // (slot reuse: block j-8 was folded, and read by block j-5, long ago)
 
     // pass 2: P = 2^(S*a - ref), packed to fp16 pairs; the P of keys [64 hf, 64 hf + 64) overwrites
     // score columns [32 hf, 32 hf + 32), which pass 2 has already consumed

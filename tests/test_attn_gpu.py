@@ -105,7 +105,7 @@ def test_core_sm_scale_argument():
 @pytest.mark.parametrize("mode,op", [("fp32", "qk_int8_sv_f16_accum_f32_attn"),
                                       ("fp16+fp32", "qk_int8_sv_f16_accum_f16_attn_inst_buf"),
                                       ("fp16", "qk_int8_sv_f16_accum_f16_attn")])
-@pytest.mark.parametrize("case", ["c2_like", "c3_like", "c4_like", "c5_like"])
+@pytest.mark.parametrize("case", ["c2_like", "c3_like", "c4_like", "c5_like", "d256"])
 def test_core_matches_reference_cuda_kernel(case, mode, op):
     """Same int8 tensors and scales into the reference's sm80 kernel (rebuilt for sm_100) and ours."""
     cuda_or_fail()
@@ -120,6 +120,9 @@ def test_core_matches_reference_cuda_kernel(case, mode, op):
     elif case == "c4_like":   # video DiT: ragged length, bf16 HND, K bias N(0, 2^2)
         args = dict(B=1, Hq=2, Hkv=2, N=2320, D=128, dtype=torch.bfloat16, layout="HND", seed=3, k_bias=2.0)
         causal = False
+    elif case == "d256":      # head_dim 256 (one query tile per CTA): GQA, ragged length, causal
+        args = dict(B=1, Hq=4, Hkv=2, N=1500, D=256, dtype=torch.bfloat16, layout="NHD", seed=5, k_bias=1.0)
+        causal = True
     else:                     # long-context causal fp16
         args = dict(B=1, Hq=4, Hkv=4, N=4096, D=128, dtype=torch.float16, layout="HND", seed=4)
         causal = True
@@ -207,7 +210,7 @@ def test_sageattn_end_to_end_vs_sdpa(layout, dtype, causal):
     max-abs <= 0.1 against SDPA-math, here for every head_dim incl. a padded one."""
     import sageattention
     cuda_or_fail()
-    for D in (64, 128, 80):
+    for D in (64, 128, 80, 200, 256):
         q, k, v = make_qkv(2, 4, 4, 1024, D, dtype, layout, seed=D)
         for mode in ("fp32", "fp16+fp32", "fp16"):
             for smooth_k in (True, False):
@@ -358,6 +361,18 @@ def test_sageattn_per_warp_granularity(mode):
     ref, _ = O.sdpa_fp32(qc, kc, vc, "HND", True)
     c = O.compare(out.cpu(), ref)
     assert c["fro_rel"] <= 0.02 and c["max_abs"] <= 0.1, c
+
+
+@pytest.mark.parametrize("mode", ["fp32", "fp16+fp32", "fp16"])
+def test_results_are_reproducible_bit_for_bit(mode):
+    """The same call gives the same bits every time, although the softmax warpgroups of a CTA run
+    unsynchronised (which CTA runs where, and how the warpgroups interleave, changes from run to run)."""
+    import sageattention
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 8, 4, 4096, 128, torch.float16, "HND", seed=51, k_bias=1.0)
+    outs = [sageattention.sageattn(q, k, v, is_causal=True, pv_accum_dtype=mode) for _ in range(5)]
+    torch.cuda.synchronize()
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
 
 
 def test_sageattn_can_be_captured_in_a_cuda_graph(monkeypatch):
