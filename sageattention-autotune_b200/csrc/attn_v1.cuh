@@ -198,9 +198,10 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 
     // Choose the reference point and the factor by which earlier work must shrink.  fp32 accumulators
     // tolerate P up to 2^8 and move the reference lazily.  The fp16 accumulators need P <= 1; their
-    // reference is the running maximum rounded UP to an integer, which still bounds P by 1, moves only
-    // when the maximum crosses an integer (rarely after the first blocks, so the rescale of O is
-    // skipped for most blocks) and makes every rescale factor an exact power of two.  The e4m3 P keeps
+    // reference is the running maximum rounded UP to a multiple of 4, which still bounds P by 1 (the
+    // largest P of a row is at least 2^-4: no loss of fp16 precision), moves only when the maximum
+    // crosses such a multiple (rarely after the first blocks, so the rescale of O is skipped for most
+    // blocks) and makes every rescale factor an exact power of two.  The e4m3 P keeps
     // the exact maximum: with three mantissa bits the rounding pattern of P depends on the reference,
     // and the published scheme (and its CPU emulation) rounds 448 * 2^(s - max).
     constexpr bool kIntRef = kF16Acc || kInstBuf;
@@ -208,11 +209,11 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     float alpha = 1.0f;
     bool rescale = false;
     if (j == 0) {
-      m_used = kIntRef ? ceilf(m_run) : m_run;
+      m_used = kIntRef ? ceilf(m_run * 0.25f) * 4.0f : m_run;
     } else {
       const float grow = m_run - m_used;
       if (kTightRef ? (grow > 0.0f) : (grow > kLazyRescale)) {
-        const float m_next = kIntRef ? ceilf(m_run) : m_run;
+        const float m_next = kIntRef ? ceilf(m_run * 0.25f) * 4.0f : m_run;
         if constexpr (kIntRef) {
           // 2^(m_used - m_next) for integer arguments, exactly; 0 below the normal range
           const int e = static_cast<int>(fmaxf(m_used - m_next, -127.0f)) + 127;

@@ -37,6 +37,7 @@ namespace sage {
 namespace v4 {
 
 constexpr int kRefRing = 8;        // block references: read by the fold warps, and three blocks later by the other softmax warpgroup
+constexpr float kRefStep = 4.0f;   // granularity of the reference exponents
 constexpr int kScaleRing = 8;      // K dequantisation scales staged by the producer, one slot per block
 constexpr int kThreads = 512;
 // setmaxnreg is a warpgroup-wide instruction: the four warps of a group must ask for the same count
@@ -179,7 +180,10 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     // the scores of block j could be issued, so the value is always the same one: results do not depend
     // on how the two warpgroups happen to interleave.
     const float r_other = (j >= 3) ? ref_ring[((j - 3) % kRefRing) * kTileQ + row] : -INFINITY;
-    const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk)), r_other);
+    // (references move in steps of kRefStep: coarse enough that the two warpgroups nearly always agree
+    // and the fold stays a plain add, fine enough that P keeps its fp16 precision: P's largest value in
+    // a row is at least 2^-kRefStep)
+    const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk * (1.0f / kRefStep)) * kRefStep), r_other);
     // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
     const float m_ref = (r_new == -INFINITY) ? 0.0f : r_new;
     const float shrink = (ref == r_new) ? 1.0f : pow2_int(fmaxf(ref - m_ref, -127.0f));
