@@ -71,12 +71,15 @@ def test_core_matches_oracle(D, dtype, layout, causal, mode):
 @pytest.mark.parametrize("N,Nkv", [(1, 1), (63, 63), (129, 129), (200, 200), (256, 256), (257, 257), (300, 1000),
                                    (1000, 300), (777, 777)])
 @pytest.mark.parametrize("causal", [False, True])
-def test_core_ragged_lengths(N, Nkv, causal):
+@pytest.mark.parametrize("mode,D", [("fp32", 128), ("fp16+fp32", 128), ("fp16+fp32", 64), ("fp16", 256)])
+def test_core_ragged_lengths(N, Nkv, causal, mode, D):
+    """Lengths from one row to several blocks, query and key lengths that differ, on both kernels
+    (one and two query tiles per CTA) and the head_dim 256 configuration; output and LSE."""
     cuda_or_fail()
-    q, k, v = make_qkv(2, 2, 2, N, 128, torch.float16, "HND", seed=N + Nkv, Nkv=Nkv, k_bias=0.5)
-    out, lse, qz = _run_core(q, k, v, "HND", causal, "fp32", return_lse=True)
-    exp, exp_lse = _oracle(qz, "HND", causal, "fp32", "per_thread", torch.float16)
-    _assert_close(out, exp, (N, Nkv, causal))
+    q, k, v = make_qkv(2, 2, 2, N, D, torch.float16, "HND", seed=N + Nkv, Nkv=Nkv, k_bias=0.5)
+    out, lse, qz = _run_core(q, k, v, "HND", causal, mode, return_lse=True)
+    exp, exp_lse = _oracle(qz, "HND", causal, mode, "per_thread", torch.float16)
+    _assert_close(out, exp, (N, Nkv, causal, mode, D))
     assert float((lse.cpu() - exp_lse).abs().max()) <= 2e-2
 
 
