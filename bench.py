@@ -36,6 +36,8 @@ WORKLOADS = {
     "c5_32k": dict(B=1, Hq=64, Hkv=64, N=32768, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
     "c5_16k": dict(B=1, Hq=64, Hkv=64, N=16384, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
     "c5_64k": dict(B=1, Hq=64, Hkv=64, N=65536, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
+    "c5_1k": dict(B=1, Hq=64, Hkv=64, N=1024, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
+    "c5_128k": dict(B=1, Hq=64, Hkv=64, N=131072, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
     "c5_4k": dict(B=1, Hq=64, Hkv=64, N=4096, D=128, dtype="float16", causal=True, pv="fp16+fp32", layout="HND", seed=4),
     "c5_8k_fp32": dict(B=1, Hq=32, Hkv=32, N=8192, D=128, dtype="float16", causal=False, pv="fp32", layout="HND", seed=4),
     "c5_32k_fp32": dict(B=1, Hq=64, Hkv=64, N=32768, D=128, dtype="float16", causal=True, pv="fp32", layout="HND", seed=4),

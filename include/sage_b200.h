@@ -191,6 +191,31 @@ int sage_b200_attn_fwd_fuse_v_mean(const int8_t* q, const int8_t* k, const void*
                                    int blk_k, int warp_q, int warp_k, int granularity, void* stream);
 
 /*
+ * The whole forward path in one call: `sageattn_qk_int8_pv_fp16_cuda` / `_sageattn_configured`
+ * (sageattention/cuda_attn.py:126-274) from the K mean to the attention kernel, i.e.
+ * sage_b200_quant_int8 (Q), sage_b200_mean_k + sage_b200_quant_int8 (K), sage_b200_cast_v_f16 when V is
+ * not fp16 (or not addressable in place) and sage_b200_attn_fwd, chained on `stream` over one
+ * caller-provided workspace of sage_b200_sageattn_workspace_bytes(...) bytes, 256-byte aligned
+ * (pass cast_v = 1 there unless V is fp16 with 16-byte aligned rows).  One foreign call per attention
+ * instead of five: at short sequences the host time of the separate calls is most of the step.
+ *   q, k, v, out  16-bit tensors by strides, already padded to head_dim 64 / 128 / 256; out has q's dtype
+ *   lse           NULL or fp32 (batch, heads_q, len_q), base 2, WITHOUT the smooth-k correction
+ *   km_out        NULL, or (batch, heads_kv, head_dim) in K's dtype: receives the K mean (callers that
+ *                 return the LSE need it for the correction q.km^T, sageattention/utils.py:39-49)
+ *   pv_accum      SAGE_B200_PV_F32, _F16 or _F16_F32
+ */
+size_t sage_b200_sageattn_workspace_bytes(int dtype, int batch, int heads_q, int heads_kv, int len_q, int len_kv,
+                                          int head_dim, int blk_q, int blk_k, int warp_q, int warp_k,
+                                          int granularity, int smooth_k, int cast_v);
+int sage_b200_sageattn(const void* q, const void* k, const void* v, void* out, float* lse, void* km_out,
+                       void* workspace, size_t workspace_bytes, int32_t* status, int dtype, int batch,
+                       int heads_q, int heads_kv, int len_q, int len_kv, int head_dim,
+                       const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                       const int64_t o_strides[3], int is_causal, float sm_scale, int blk_q, int blk_k,
+                       int warp_q, int warp_k, int granularity, int smooth_k, int pv_accum, int div_mode,
+                       void* stream);
+
+/*
  * V in fp8 e4m3 with one fp32 scale per (batch, head, channel): scale = max|v| over the sequence / 448,
  * v_fp8 = e4m3(v / scale), round to nearest, saturating.  The reference has no fp8 path in this
  * tree (sageattention/core.py:18-21 exports sageattn_qk_int8_pv_fp8_cuda = None; the kernels live on

@@ -25,6 +25,7 @@ EXPORTS = (
     "sage_b200_quant_int8", "sage_b200_smooth_quant_k_scratch_bytes", "sage_b200_smooth_quant_k",
     "sage_b200_cast_v_f16", "sage_b200_attn_fwd", "sage_b200_quant_v_fp8_scratch_bytes", "sage_b200_quant_v_fp8",
     "sage_b200_attn_fwd_fp8", "sage_b200_smooth_v_f16", "sage_b200_attn_fwd_fuse_v_mean",
+    "sage_b200_sageattn_workspace_bytes", "sage_b200_sageattn",
 )
 
 _lib = None
@@ -77,6 +78,11 @@ def lib() -> ctypes.CDLL:
         L.sage_b200_attn_fwd_fuse_v_mean.restype = i
         L.sage_b200_attn_fwd_fuse_v_mean.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i,
                                                      i64p, i64p, i64p, i64p, i, f, i, i, i, i, i, vp]
+        L.sage_b200_sageattn_workspace_bytes.restype = ctypes.c_size_t
+        L.sage_b200_sageattn_workspace_bytes.argtypes = [i] * 14
+        L.sage_b200_sageattn.restype = i
+        L.sage_b200_sageattn.argtypes = [vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp, i, i, i, i, i, i, i,
+                                         i64p, i64p, i64p, i64p, i, f, i, i, i, i, i, i, i, i, vp]
         _lib = L
     return _lib
 

@@ -141,6 +141,51 @@ def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_
     return lse
 
 
+def _sageattn_one_call(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, return_lse, qk_config,
+                       sm_scale, qk_quant_gran, head_dim):
+    """The path of _sageattn_configured through the single C entry point sage_b200_sageattn: one
+    workspace allocation and one foreign call instead of five.  Inputs are already padded and aligned."""
+    blk_q, blk_k, warp_q, warp_k = qk_config
+    if qk_quant_gran == "per_warp":
+        blk_q, warp_k, qk_quant_gran = warp_q, blk_k, "per_block"
+    gran = C.GRAN_PER_THREAD if qk_quant_gran == "per_thread" else C.GRAN_PER_BLOCK
+    b, hq, nq, d = C.bhnd(q, tensor_layout)
+    _, hkv, nk, _ = C.bhnd(k, tensor_layout)
+    dev = q.device
+    L = C.lib()
+    dt = C.dtype_code(q.dtype)
+    cast_v = 0 if v.dtype == torch.float16 else 1
+    nbytes = L.sage_b200_sageattn_workspace_bytes(dt, b, hq, hkv, nq, nk, d, blk_q, blk_k, warp_q, warp_k, gran,
+                                                  1 if smooth_k else 0, cast_v)
+    work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    output = torch.empty(q.size(), dtype=q.dtype, device=dev)
+    lse = torch.empty((b, hq, nq), dtype=torch.float32, device=dev) if return_lse else None
+    km = None
+    if return_lse and smooth_k:
+        km = torch.empty((b, hkv, 1, d) if tensor_layout == "HND" else (b, 1, hkv, d), dtype=k.dtype, device=dev)
+    check = _check_status_enabled()
+    status = torch.zeros(4, dtype=torch.int32, device=dev) if check else None
+    with torch.cuda.device(dev):
+        C.check(L.sage_b200_sageattn(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(), lse.data_ptr() if return_lse else 0,
+            km.data_ptr() if km is not None else 0, work.data_ptr(), nbytes, status.data_ptr() if check else 0,
+            dt, b, hq, hkv, nq, nk, d, C.bhn_strides(q, tensor_layout), C.bhn_strides(k, tensor_layout),
+            C.bhn_strides(v, tensor_layout), C.bhn_strides(output, tensor_layout), 1 if is_causal else 0,
+            float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran, 1 if smooth_k else 0, _PV_CODE[pv_accum_dtype],
+            Q._DIV[Q.default_div_mode()], C.stream_ptr(dev)))
+    if check:
+        st = status.tolist()
+        if st[0] != 0:
+            raise C.SageB200Error(f"attention kernel gave up waiting (code {st[0]}) in CTA {tuple(st[1:])}")
+    output = output[..., :head_dim]
+    if not return_lse:
+        return output
+    lse = lse / LOG2_E
+    if smooth_k:
+        lse = lse + _lse_correction(q, km, tensor_layout) * sm_scale
+    return output, lse
+
+
 def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v, return_lse,
                          qk_config, sm_scale: Optional[float] = None, qk_quant_gran: str = "per_thread"):
     """Same contract as the reference's _sageattn_configured (cuda_attn.py:126-274)."""
@@ -181,6 +226,9 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
     q, k, v = _aligned(q), _aligned(k), _aligned(v)
 
     blk_q, blk_k, warp_q, warp_k = qk_config
+    if _profile is None and not smooth_v and pv_accum_dtype in _PV_CODE:
+        return _sageattn_one_call(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, return_lse,
+                                  qk_config, sm_scale, qk_quant_gran, head_dim)
     if qk_quant_gran == "per_warp":
         # one scale per WARPQ query rows and per BLKK keys: the per-block scheme with WARPQ-row Q blocks
         blk_q, qk_config, qk_quant_gran = warp_q, (warp_q, blk_k, warp_q, blk_k), "per_block"
