@@ -105,7 +105,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except OSError:
@@ -113,9 +113,12 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples that arrived between the two host times (all of them when not given).
+        The sampler is started before the warm-up so that nvidia-smi is already running when the timed
+        region begins; only what it printed during that region counts."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -125,7 +128,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for ln in self.lines:
+        for stamp, ln in self.lines:
+            if t_begin is not None and not (t_begin <= stamp <= t_end + 0.03):
+                continue
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 7:
                 continue
@@ -259,14 +264,15 @@ def main():
 
     warmup = max(3, args.warmup)
     sampler = ClockSampler(local_rank)
+    sampler.start()
     # ---- device-resident throughput, with per-kernel events collected over the timed steps
     for _ in range(warmup):
         step()
     barrier()
     sa_core._profile = []
-    sampler.start()
+    t_begin = time.perf_counter()
     total_ms = timed(step, args.steps, 0)
-    clocks = sampler.stop()
+    clocks = sampler.stop(t_begin, time.perf_counter())
     prof, sa_core._profile = sa_core._profile, None
     per_label = {}
     for label, s, e in prof:
