@@ -73,3 +73,71 @@ def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout:
     if want_lse:
         return out_full, gather_heads(lse, 1)
     return out_full
+
+
+# ---------------------------------------------------------------------------------------------------
+# (batch x kv-head) grid sharding: for shapes whose head count does not divide over the GPUs
+# (16 x 10 heads on 8 GPUs) the ranks form a wb x wh grid and each owns a rectangle of batches and
+# kv-heads.  The grid is the factorisation of the world size that leaves the busiest rank the least
+# work; with batch 1 it reduces to the head sharding above.
+# ---------------------------------------------------------------------------------------------------
+def shard_grid(batch: int, num_kv_heads: int, world_size: int) -> Tuple[int, int]:
+    """(wb, wh) with wb * wh == world_size minimising ceil(batch/wb) * ceil(num_kv_heads/wh);
+    ties go to the grid with more head shards."""
+    if batch <= 0 or num_kv_heads <= 0 or world_size <= 0:
+        raise ValueError("bad shard request")
+    best = None
+    for wb in range(1, world_size + 1):
+        if world_size % wb:
+            continue
+        wh = world_size // wb
+        load = -(-batch // wb) * -(-num_kv_heads // wh)
+        if best is None or load < best[0] or (load == best[0] and wh > best[2]):
+            best = (load, wb, wh)
+    return best[1], best[2]
+
+
+def local_block(batch: int, num_q_heads: int, num_kv_heads: int, world_size: int, rank: int):
+    """(batch_range, q_head_range, kv_head_range) of this rank in the grid of `shard_grid`
+    (rank = ib * wh + ih)."""
+    if num_q_heads % num_kv_heads:
+        raise ValueError("num_qo_heads must be divisible by num_kv_heads")
+    wb, wh = shard_grid(batch, num_kv_heads, world_size)
+    ib, ih = divmod(rank, wh)
+    rep = num_q_heads // num_kv_heads
+    b_lo, b_hi = shard_range(batch, wb, ib)
+    k_lo, k_hi = shard_range(num_kv_heads, wh, ih)
+    return (b_lo, b_hi), (k_lo * rep, k_hi * rep), (k_lo, k_hi)
+
+
+def slice_block(t: torch.Tensor, tensor_layout: str, b_range, h_range) -> torch.Tensor:
+    return slice_heads(t[b_range[0]:b_range[1]], tensor_layout, h_range[0], h_range[1])
+
+
+def gather_blocks(out_local: torch.Tensor, batch: int, num_q_heads: int, num_kv_heads: int,
+                  tensor_layout: str = "HND", group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gather of the rectangles of `local_block` into the full (batch, ..., heads, ...) output on every
+    rank: one NCCL all-gather of equal-sized slots, then one copy per rank's rectangle."""
+    world = dist.get_world_size(group)
+    wb, wh = shard_grid(batch, num_kv_heads, world)
+    rep = num_q_heads // num_kv_heads
+    pb, ph = -(-batch // wb), -(-num_kv_heads // wh) * rep
+    h_dim = 1 if tensor_layout == "HND" else 2
+    full_shape = list(out_local.shape)
+    full_shape[0], full_shape[h_dim] = batch, num_q_heads
+    slot_shape = list(out_local.shape)
+    slot_shape[0], slot_shape[h_dim] = pb, ph
+    slot = torch.zeros(slot_shape, dtype=out_local.dtype, device=out_local.device)
+    if out_local.numel():
+        slice_heads(slot[: out_local.size(0)], tensor_layout, 0, out_local.size(h_dim)).copy_(out_local)
+    cat_shape = list(slot_shape)
+    cat_shape[0] = world * pb                        # slots concatenated along the batch dimension
+    gathered = torch.empty(cat_shape, dtype=out_local.dtype, device=out_local.device)
+    dist.all_gather_into_tensor(gathered, slot, group=group)
+    full = torch.empty(full_shape, dtype=out_local.dtype, device=out_local.device)
+    for r in range(world):
+        (b_lo, b_hi), (q_lo, q_hi), _ = local_block(batch, num_q_heads, num_kv_heads, world, r)
+        if b_hi > b_lo and q_hi > q_lo:
+            src = slice_heads(gathered[r * pb: r * pb + (b_hi - b_lo)], tensor_layout, 0, q_hi - q_lo)
+            slice_heads(full[b_lo:b_hi], tensor_layout, q_lo, q_hi).copy_(src)
+    return full

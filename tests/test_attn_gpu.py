@@ -403,3 +403,52 @@ def test_sageattn_can_be_captured_in_a_cuda_graph(monkeypatch):
     eager = sageattention.sageattn(q2, k2, v2, **kw)
     assert torch.equal(out_g, eager)
 
+
+def test_random_shapes_agree_across_accumulate_modes():
+    """150 seeded random problems (batch, GQA ratio, lengths from 1 to 6000 with unequal query/key
+    lengths, head_dim incl. padded ones and 256, both layouts and dtypes, causal or not, LSE or not):
+    every mode finishes with a clean status word, finite output, and agrees with the fp32 mode."""
+    import random
+    import sageattention
+    cuda_or_fail()
+    rng = random.Random(1234)
+    for _ in range(150):
+        B = rng.choice([1, 1, 2, 3])
+        Hkv = rng.choice([1, 2, 4, 8])
+        Hq = Hkv * rng.choice([1, 1, 2, 4])
+        D = rng.choice([64, 128, 128, 128, 256, 96, 40])
+        N = rng.choice([1, 7, 64, 127, 128, 129, 255, 256, 300, 511, 777, 1024, 1500, 2049, 4096, 6000])
+        Nkv = N if rng.random() < 0.8 else rng.choice([64, 200, 1000, 3000])
+        dtype = rng.choice([torch.float16, torch.bfloat16])
+        layout = rng.choice(["HND", "NHD"])
+        causal = rng.random() < 0.5
+        mode = rng.choice(["fp16+fp32", "fp16+fp32", "fp16"])
+        gen = torch.Generator(device="cuda").manual_seed(rng.randrange(1 << 30))      # on the device: this test is about shapes
+        shp = (lambda h, n: (B, h, n, D)) if layout == "HND" else (lambda h, n: (B, n, h, D))
+        q = torch.randn(shp(Hq, N), device="cuda", generator=gen).to(dtype)
+        k = (torch.randn(shp(Hkv, Nkv), device="cuda", generator=gen) + rng.choice([0.0, 2.0])).to(dtype)
+        v = torch.randn(shp(Hkv, Nkv), device="cuda", generator=gen).to(dtype)
+        out = sageattention.sageattn(q, k, v, tensor_layout=layout, is_causal=causal, pv_accum_dtype=mode,
+                                     return_lse=rng.random() < 0.3)
+        out = out[0] if isinstance(out, tuple) else out
+        ref = sageattention.sageattn(q, k, v, tensor_layout=layout, is_causal=causal, pv_accum_dtype="fp32")
+        what = (B, Hq, Hkv, N, Nkv, D, dtype, layout, causal, mode)
+        assert bool(torch.isfinite(out.float()).all()), what
+        c = O.compare(out.float().cpu(), ref.float().cpu())
+        assert c["cos"] > 0.9995, (what, c)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "fp16+fp32", "fp16"])
+def test_extreme_score_ranges(mode):
+    """Scores spread over hundreds of binades (large inputs, sm_scale = 1): the running maximum jumps by
+    far more than fp16 or the rescale factors can represent between blocks, rows become one-hot, and
+    factors underflow to zero.  Output and LSE must still follow the oracle."""
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 2, 2, 1024, 128, torch.float16, "HND", seed=61)
+    q, k = q * 4.0, k * 4.0
+    out, lse, qz = _run_core(q, k, v, "HND", True, mode, sm_scale=1.0, return_lse=True)
+    exp, exp_lse = _oracle(qz, "HND", True, mode, "per_thread", torch.float16, sm_scale=1.0)
+    assert bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(lse).all())
+    _assert_close(out, exp, ("extreme", mode))
+    assert float(((lse.cpu() - exp_lse).abs() / exp_lse.abs().clamp_min(1.0)).max()) <= 1e-3
+
