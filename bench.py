@@ -293,7 +293,7 @@ def main():
                 "unit": "TFLOP/s", "frac": (achieved / peak_mixed) if achieved else None,
                 # dram__bytes_read+write of an ncu capture at N=4096, H=64 (profiles/attn_fwd_fp16fp32_c5_4k.md),
                 # scaled by the number of Q/K/V/O elements of this rank (all terms are linear in them)
-                "traffic": 182.1e6 * (w["B"] * heads_local * w["N"] * w["D"]) / (64 * 4096 * 128) if w["D"] == 128 else None,
+                "traffic": 179.0e6 * (w["B"] * heads_local * w["N"] * w["D"]) / (64 * 4096 * 128) if w["D"] == 128 else None,
                 "traffic_unit": "bytes per launch (scaled from a 4k capture)",
                 "peak_source": f"{pk['source']}: 4/3 x sustained dense bf16 ({pk['bf16_sustained']} TF/s); int8 counted at 2x bf16",
                 "frac_of_int8_peak_literal": (literal_flops(w, heads_local) / (attn_ms * 1e-3) / 1e12) / (2 * pk["bf16_sustained"]) if attn_ms else None,
