@@ -19,9 +19,9 @@
 // A softmax thread reads its scores twice, 64 columns at a time (pass 1: maximum, pass 2: exponentials),
 // instead of holding 128 of them: that keeps it at 144 registers and leaves 184 for a fold thread.
 // The two softmax warpgroups never wait for one another: each keeps its own reference exponent and row
-// sum.  A reference is an INTEGER r >= the running maximum of the blocks its warpgroup has seen, so
-// P = 2^(s - r) <= 1 as the fp16 partial product requires, and every factor between two references
-// is an exact power of two.  Each block's reference travels to the fold warps, which keep the output's
+// sum.  A reference is an INTEGER (a multiple of kRefStep) r >= the running maximum of the blocks its
+// warpgroup has seen, so P = 2^(s - r) <= 1 as the fp16 partial product requires, and every factor
+// between two references is an exact power of two.  Each block's reference travels to the fold warps, which keep the output's
 // own reference (the largest seen so far) and apply alpha = 2^(r_O - r_new) to O and
 // beta = 2^(r_block - r_new) to T; when both are 1 for a whole warp the fold is a plain add.  To keep
 // that the common case a warpgroup also folds the other's reference of three blocks earlier into its
