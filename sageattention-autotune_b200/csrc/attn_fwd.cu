@@ -53,14 +53,15 @@ static int make_map(CUtensorMap* map, const void* base, int elem_bytes, int batc
   return SAGE_B200_OK;
 }
 
-template <int D, int PV_MODE, int OUT_DTYPE>
+template <int D, int PV_MODE, int OUT_DTYPE, int KSUB>
 static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                        dim3 grid, cudaStream_t stream) {
   // Two kernels exist.  fp32, fp16 and fp8 accumulation run the two-tile kernel (attn_v1.cuh: 256 query
   // rows per CTA share every K/V block, the output accumulates in tensor memory).  The two-level
   // "fp16+fp32" mode needs an fp16 partial product next to the scores and runs the one-tile kernel with
   // a fold warpgroup (attn_v4.cuh); SAGE_B200_KERNEL=coupled runs it on the two-tile kernel instead,
-  // which folds inside the softmax warps (slower, kept as a cross-check).
+  // which folds inside the softmax warps (slower, kept as a cross-check).  KSUB = 2 (scale blocks of
+  // 32 keys, the reference's (128, 32, 32, 32) candidate) is built into the two-tile kernel only.
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams) = nullptr;
   int smem = 0;
   int threads = kAttnThreads;
@@ -70,10 +71,10 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       const char* e = getenv("SAGE_B200_KERNEL");
       return e != nullptr && e[0] == 'c';
     }();
-    if constexpr (D == 256) {
+    if constexpr (D == 256 || KSUB != 1) {
       // 256 channels of fp16 partial product and of fp32 output do not fit the one-tile kernel's
       // tensor memory and registers: the mode folds 64 channels at a time inside the softmax warps
-      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
+      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
       smem = v1::SmemPlan<D>::kDynamic;
     } else if (two_tile) {
       kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
@@ -86,14 +87,14 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       which = 1;
     }
   } else if constexpr (PV_MODE == SAGE_B200_PV_F8) {
-    if constexpr (D == 256) {
-      return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: the fp8 P.V mode is built for head_dim 64 and 128 only");
+    if constexpr (D == 256 || KSUB != 1) {
+      return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: the fp8 P.V mode is built for head_dim 64 and 128 and 64-key scale blocks only");
     } else {
       kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
       smem = v1::SmemPlan<D, true>::kDynamic;
     }
   } else {
-    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
+    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
     smem = v1::SmemPlan<D>::kDynamic;
   }
   cudaError_t attr_err = cudaSuccess;
@@ -116,21 +117,21 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   return SAGE_B200_OK;
 }
 
-template <int D, int PV_MODE>
+template <int D, int PV_MODE, int KSUB>
 static int launch_attn_out(int out_dtype, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                            const AttnParams& p, dim3 grid, cudaStream_t stream) {
-  if (out_dtype == SAGE_B200_BF16) return launch_attn<D, PV_MODE, SAGE_B200_BF16>(mq, mk, mv, p, grid, stream);
-  return launch_attn<D, PV_MODE, SAGE_B200_F16>(mq, mk, mv, p, grid, stream);
+  if (out_dtype == SAGE_B200_BF16) return launch_attn<D, PV_MODE, SAGE_B200_BF16, KSUB>(mq, mk, mv, p, grid, stream);
+  return launch_attn<D, PV_MODE, SAGE_B200_F16, KSUB>(mq, mk, mv, p, grid, stream);
 }
 
-template <int D>
+template <int D, int KSUB>
 static int launch_attn_mode(int pv_accum, int out_dtype, const CUtensorMap& mq, const CUtensorMap& mk,
                             const CUtensorMap& mv, const AttnParams& p, dim3 grid, cudaStream_t stream) {
   switch (pv_accum) {
-    case SAGE_B200_PV_F32: return launch_attn_out<D, SAGE_B200_PV_F32>(out_dtype, mq, mk, mv, p, grid, stream);
-    case SAGE_B200_PV_F16: return launch_attn_out<D, SAGE_B200_PV_F16>(out_dtype, mq, mk, mv, p, grid, stream);
-    case SAGE_B200_PV_F8: return launch_attn_out<D, SAGE_B200_PV_F8>(out_dtype, mq, mk, mv, p, grid, stream);
-    default: return launch_attn_out<D, SAGE_B200_PV_F16_F32>(out_dtype, mq, mk, mv, p, grid, stream);
+    case SAGE_B200_PV_F32: return launch_attn_out<D, SAGE_B200_PV_F32, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
+    case SAGE_B200_PV_F16: return launch_attn_out<D, SAGE_B200_PV_F16, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
+    case SAGE_B200_PV_F8: return launch_attn_out<D, SAGE_B200_PV_F8, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
+    default: return launch_attn_out<D, SAGE_B200_PV_F16_F32, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
   }
 }
 
@@ -172,12 +173,13 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   if (head_dim == 256 && pv_accum == SAGE_B200_PV_F8)
     return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: the fp8 P.V mode is built for head_dim 64 and 128 only");
   SAGE_REQUIRE(blk_q == 32 || blk_q == 64 || blk_q == 128, "attn_fwd: blk_q must be 32, 64 or 128");
-  if (blk_k != 64)
-    return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: only blk_k = 64 scale blocks are built (got %d)", blk_k);
+  SAGE_REQUIRE(blk_k == 64 || blk_k == 32, "attn_fwd: blk_k must be 64 or 32, got %d", blk_k);
+  if (blk_k == 32 && (head_dim == 256 || pv_accum == SAGE_B200_PV_F8))
+    return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: 32-key scale blocks are built for head_dim 64 and 128 and the fp16-V modes");
   if (granularity == SAGE_B200_GRAN_PER_THREAD) {
     SAGE_REQUIRE(warp_q >= 8 && warp_q <= blk_q && (warp_q & (warp_q - 1)) == 0, "attn_fwd: bad warp_q %d", warp_q);
-    if (warp_k != 64)
-      return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: only warp_k = 64 is built (got %d)", warp_k);
+    if (warp_k != blk_k)
+      return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: only warp_k = blk_k is built (got %d, %d)", warp_k, blk_k);
   }
   SAGE_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15u) == 0 && o_strides[0] % 8 == 0 && o_strides[1] % 8 == 0 &&
                    o_strides[2] % 8 == 0, "attn_fwd: output must be 16-byte aligned with strides % 8 == 0");
@@ -232,9 +234,13 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
 
   const int rows_per_cta = (head_dim == 256 ? 1 : 2) * kTileQ;     // the one-tile kernel resets grid.x itself
   const dim3 grid((len_q + rows_per_cta - 1) / rows_per_cta, heads_q, batch);
-  if (head_dim == 64) return launch_attn_mode<64>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
-  if (head_dim == 256) return launch_attn_mode<256>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
-  return launch_attn_mode<128>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+  if (blk_k == 32) {
+    if (head_dim == 64) return launch_attn_mode<64, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+    return launch_attn_mode<128, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+  }
+  if (head_dim == 64) return launch_attn_mode<64, 1>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+  if (head_dim == 256) return launch_attn_mode<256, 1>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+  return launch_attn_mode<128, 1>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
 }
 
 

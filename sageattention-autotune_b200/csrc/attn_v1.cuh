@@ -70,10 +70,13 @@ struct SmemPlan {
 };
 
 
-__device__ __forceinline__ int k_class(int c) { return ((c >> 6) << 2) | ((c & 7) >> 1); }
+// Scale class of column c of a 128-key block.  KSUB = 64 / BLKK scale blocks per 64 keys: the reference's
+// candidates use BLKK = WARPK = 64 (eight classes per block) or 32 (sixteen).
+template <int KSUB>
+__device__ __forceinline__ constexpr int k_class(int c) { return ((c / (64 / KSUB)) << 2) | ((c & 7) >> 1); }
 
 // One softmax warpgroup: thread `row` (0..127) of tile `tile`.
-template <int D, int PV_MODE, int OUT_DTYPE>
+template <int D, int PV_MODE, int OUT_DTYPE, int KSUB>
 __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars, uint32_t tmem_base,
                                              volatile int* abort_flag, int tile, int row, int n_blocks,
                                              int q_row0, int b, int h, int h_kv) {
@@ -103,46 +106,37 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
   float m_used = -INFINITY;    // reference point P and O are expressed against
   float d_sum = 0.0f;
   bool ok = true;
-  // scales of the two 64-key halves of block j (vector loads: the groups of one half are contiguous)
+  // scales of block j: four per scale block of 64 / KSUB keys in the per-thread layout (vector loads),
+  // one per scale block in the per-block layout (replicated over the four classes)
+  constexpr int kNA = 8 * KSUB;
   const bool per_thread = (p.gran == SAGE_B200_GRAN_PER_THREAD);
-  auto load_scales = [&](int j, float4& lo, float4& hi) {
-    lo = make_float4(0.f, 0.f, 0.f, 0.f);
-    hi = lo;
-    if (per_thread) {
-      if (j * 8 + 3 < p.k_groups)
-        asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "l"(ks_base + 8 * j));
-      if (j * 8 + 7 < p.k_groups)
-        asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w) : "l"(ks_base + 8 * j + 4));
-    } else {
-      if (2 * j < p.k_groups) {
-        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(lo.x) : "l"(ks_base + 2 * j));
-        lo.y = lo.z = lo.w = lo.x;
+  auto load_scales = [&](int j, float (&a)[kNA]) {
+#pragma unroll
+    for (int u = 0; u < 2 * KSUB; ++u) {
+      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (per_thread) {
+        if (j * kNA + 4 * u + 3 < p.k_groups)
+          asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(f.x), "=f"(f.y), "=f"(f.z), "=f"(f.w) : "l"(ks_base + kNA * j + 4 * u));
+      } else if (2 * KSUB * j + u < p.k_groups) {
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(f.x) : "l"(ks_base + 2 * KSUB * j + u));
+        f.y = f.z = f.w = f.x;
       }
-      if (2 * j + 1 < p.k_groups) {
-        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(hi.x) : "l"(ks_base + 2 * j + 1));
-        hi.y = hi.z = hi.w = hi.x;
-      }
+      a[4 * u + 0] = f.x, a[4 * u + 1] = f.y, a[4 * u + 2] = f.z, a[4 * u + 3] = f.w;
     }
   };
 
 #pragma unroll 1
   for (int j = 0; j < n_blocks; ++j) {
     const int k0 = j * kBlockKV;
-    // the eight dequantisation constants of this block; the next block's line is pulled into L1 now
+    // the 8 * KSUB dequantisation constants of this block; the next block's line is pulled into L1 now
     // so that its loads do not pay an L2 round trip (registers are too scarce to hold them a block ahead)
-    float a[8];
-    {
-      float4 lo, hi;
-      load_scales(j, lo, hi);
-      if (j + 1 < n_blocks)
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(ks_base + (per_thread ? 8 : 2) * (j + 1)));
-      a[0] = lo.x, a[1] = lo.y, a[2] = lo.z, a[3] = lo.w;
-      a[4] = hi.x, a[5] = hi.y, a[6] = hi.z, a[7] = hi.w;
-    }
+    float a[kNA];
+    load_scales(j, a);
+    if (j + 1 < n_blocks)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(ks_base + (per_thread ? kNA : 2 * KSUB) * (j + 1)));
 #pragma unroll
-    for (int t = 0; t < 8; ++t) a[t] = p.scale_log2 * (q_sc * a[t]);
+    for (int t = 0; t < kNA; ++t) a[t] = p.scale_log2 * (q_sc * a[t]);
 
     if (row == 0) SAGE_TR(tile, 1, j);
     ok = wait_bar_warp(bar_s_full, j & 1, abort_flag, 10 + tile);
@@ -167,18 +161,20 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 #pragma unroll
       for (int c = 0; c < 128; ++c) s[c] += kMagicI;
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const int base = (t >> 2) * 64 + (t & 3) * 2;       // the class owns columns base + 8i, base + 8i + 1
-        float v[16];
+      for (int t = 0; t < kNA; ++t) {
+        constexpr int kSpan = 64 / KSUB;                    // keys per scale block
+        constexpr int kVals = kSpan / 4;                    // columns of one class in it
+        const int base = (t >> 2) * kSpan + (t & 3) * 2;    // the class owns columns base + 8i, base + 8i + 1
+        float v[kVals];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < kVals / 2; ++i) {
           v[2 * i] = __uint_as_float(s[base + 8 * i]);
           v[2 * i + 1] = __uint_as_float(s[base + 8 * i + 1]);
         }
         float mx = v[0];
 #pragma unroll
-        for (int i = 1; i < 15; i += 2) mx = ptx::max3(mx, v[i], v[i + 1]);
-        mx = fmaxf(mx, v[15]);
+        for (int i = 1; i < kVals - 1; i += 2) mx = ptx::max3(mx, v[i], v[i + 1]);
+        mx = fmaxf(mx, v[kVals - 1]);
         m_blk = fmaxf(m_blk, (mx - kMagicF) * a[t]);
       }
     } else {
@@ -188,7 +184,7 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       const int lim = min(lim_causal, lim_len);
 #pragma unroll
       for (int c = 0; c < 128; ++c) {
-        float x = static_cast<float>(static_cast<int>(s[c])) * a[k_class(c)];
+        float x = static_cast<float>(static_cast<int>(s[c])) * a[k_class<KSUB>(c)];
         x = (c <= lim) ? x : -INFINITY;
         m_blk = fmaxf(m_blk, x);
         s[c] = __float_as_uint(x);
@@ -279,20 +275,37 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     constexpr int kPolyNum = kInstBuf ? 2 : SAGE_V1_POLY;
     if (!need_mask) {
       // p = 2^(X*a + neg) with neg = -(1.5*2^23*a + m); two columns of one class per packed FMA
-      unsigned long long a2[8], neg2[8];
+      // (with sixteen classes the packed constants are built per scale block of 32 keys: holding all of
+      // them would cost 64 registers)
+      constexpr int kHeld = (KSUB == 1) ? 8 : 4;
+      unsigned long long a2[kHeld], neg2[kHeld];
+      if constexpr (KSUB == 1) {
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const float ng = fmaf(-kMagicF, a[t], -m_ref);
-        a2[t] = ptx::pack2(a[t], a[t]);
-        neg2[t] = ptx::pack2(ng, ng);
+        for (int t = 0; t < 8; ++t) {
+          const float ng = fmaf(-kMagicF, a[t], -m_ref);
+          a2[t] = ptx::pack2(a[t], a[t]);
+          neg2[t] = ptx::pack2(ng, ng);
+        }
       }
       unsigned long long acc0 = ptx::pack2(0.0f, 0.0f), acc1 = acc0;
 #pragma unroll
       for (int c = 0; c < 128; c += 4) {
+        if constexpr (KSUB == 2) {
+          if ((c & 31) == 0) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float at = a[(c >> 5) * 4 + t];
+              const float ng = fmaf(-kMagicF, at, -m_ref);
+              a2[t] = ptx::pack2(at, at);
+              neg2[t] = ptx::pack2(ng, ng);
+            }
+          }
+        }
+        constexpr int kMask = (KSUB == 1) ? 7 : 3;          // index into the constants that are held
         const unsigned long long e0 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 0]), __uint_as_float(s[c + 1])),
-                                                a2[k_class(c)], neg2[k_class(c)]);
+                                                a2[k_class<KSUB>(c) & kMask], neg2[k_class<KSUB>(c) & kMask]);
         const unsigned long long e1 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])),
-                                                a2[k_class(c + 2)], neg2[k_class(c + 2)]);
+                                                a2[k_class<KSUB>(c + 2) & kMask], neg2[k_class<KSUB>(c + 2) & kMask]);
         float p0, p1, p2, p3;
         if (((c >> 2) % kPolyDen) < kPolyNum) {
           ptx::exp2_pair_poly(e0, p0, p1);
@@ -450,7 +463,7 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
   ptx::tc_fence_before();
 }
 
-template <int D, int PV_MODE, int OUT_DTYPE>
+template <int D, int PV_MODE, int OUT_DTYPE, int KSUB = 1>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -520,7 +533,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (warp < 8) {
     ptx::reg_inc<232>();
     const int tile = warp >> 2;
-    softmax_role<D, PV_MODE, OUT_DTYPE>(p, bars, tmem_base, abort_flag, tile, threadIdx.x & 127, n_blk[tile],
+    softmax_role<D, PV_MODE, OUT_DTYPE, KSUB>(p, bars, tmem_base, abort_flag, tile, threadIdx.x & 127, n_blk[tile],
                                         q0 + tile * kTileQ, b, h, h_kv);
   } else {
     ptx::reg_dec<40>();

@@ -2,8 +2,8 @@
 
 The reference times four (BLKQ, BLKK, WARPQ, WARPK) candidates per shape at run time
 (sageattention/cuda_autotune.py:9-77) because its sm80 kernel's best CTA shape depends on the
-GPU.  The sm_100a kernel has one CTA shape - two 128-row query tiles against 128-key blocks -
-and what the tuple still decides is which rows and keys share an int8 scale, which must be the
+GPU.  The sm_100a kernels fix their CTA shape per accumulate mode (128-row query tiles against
+128-key blocks), and what the tuple still decides is which rows and keys share an int8 scale, which must be the
 same in the quantiser and in the attention kernel.  The table therefore maps
 (head_dim, causal, pv_accum_dtype, sequence bucket) to the scale grouping; today every entry is
 the reference's first candidate and fallback, (128, 64, 32, 64), which keeps results comparable
@@ -19,8 +19,9 @@ QK_CONFIGS = (
 )
 DEFAULT_QK_CONFIG = QK_CONFIGS[0]
 
-# groupings the sm_100a attention kernel consumes (BLKK = WARPK = 64)
-SUPPORTED_QK_CONFIGS = tuple(c for c in QK_CONFIGS if c[1] == 64 and c[3] == 64)
+# groupings the sm_100a attention kernels consume: BLKK = WARPK = 64 or 32, i.e. all four (with 32-key
+# blocks not for head_dim 256 or the fp8 P.V variant)
+SUPPORTED_QK_CONFIGS = tuple(c for c in QK_CONFIGS if c[1] == c[3] and c[1] in (32, 64))
 
 _SEQ_BUCKETS = (1024, 4096, 16384, 65536)
 

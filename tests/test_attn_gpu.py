@@ -140,6 +140,46 @@ def test_core_matches_reference_cuda_kernel(case, mode, op):
     print(case, mode, c)
 
 
+@pytest.mark.parametrize("mode,op", [("fp32", "qk_int8_sv_f16_accum_f32_attn"),
+                                      ("fp16+fp32", "qk_int8_sv_f16_accum_f16_attn_inst_buf"),
+                                      ("fp16", "qk_int8_sv_f16_accum_f16_attn")])
+@pytest.mark.parametrize("D,dtype,layout,N", [(128, torch.bfloat16, "HND", 2320), (64, torch.float16, "NHD", 1024)])
+def test_32_key_scale_blocks_match_reference_cuda_kernel(D, dtype, layout, N, mode, op):
+    """The reference's (BLKQ, BLKK, WARPQ, WARPK) = (128, 32, 32, 32) candidate: K scales per 32 keys
+    (sixteen scale classes per 128-key block).  Non-causal against the reference kernel (it accepts this
+    configuration for non-causal attention only), causal and non-causal against the oracle."""
+    from sageattention import quant
+    from sageattention.core import attn_fwd_quantized
+    cuda_or_fail()
+    ref = reference_ops()
+    assert ref is not None, "oracle/_ref/libsage_ref_sm80.so is missing: run make -C oracle"
+    cfg = (128, 32, 32, 32)
+    q, k, v = make_qkv(1, 4, 2, N, D, dtype, layout, seed=71, k_bias=1.5)
+    km = quant.mean_k(k, layout)
+    q8, qs, k8, ks = quant.per_thread_int8(q, k, km, 128, 32, 32, 32, layout, div="ieee")
+    v16 = quant.cast_v_fp16(v, layout)
+    for causal in (False, True):
+        out = torch.empty_like(q)
+        lse = attn_fwd_quantized(q8, k8, v16, out, qs, ks, layout, causal, D ** -0.5, cfg, mode, True)
+        torch.cuda.synchronize()
+        exp, exp_lse = O.attend(q8.cpu(), k8.cpu(), v16.cpu(), qs.cpu(), ks.cpu(), layout, causal, None, mode,
+                                "per_thread", 128, 32, 32, 32, dtype, True)
+        _assert_close(out, exp, ("blk_k 32 vs oracle", D, causal, mode))
+        assert float((lse.cpu() - exp_lse).abs().max()) <= 2e-2
+        if not causal:
+            ref_out = torch.empty_like(q)
+            getattr(ref, op)(q8, k8, v16, ref_out, qs, ks, 0 if layout == "NHD" else 1, False, D ** -0.5, *cfg, False)
+            torch.cuda.synchronize()
+            _assert_close(out, ref_out, ("blk_k 32 vs reference", D, mode))
+    # the per-block scheme with 32-key blocks, through the public call
+    import sageattention
+    from sageattention.core import _sageattn_configured
+    o_blk = _sageattn_configured(q, k, v, layout, False, mode, True, False, False, cfg, None, "per_block")
+    exp_blk, _ = O.sdpa_fp32(q.cpu(), k.cpu(), v.cpu(), layout, False)
+    c = O.compare(o_blk.cpu(), exp_blk)
+    assert c["fro_rel"] <= 0.02 and c["max_abs"] <= 0.1, c
+
+
 @pytest.mark.parametrize("case", ["c2_like", "c3_like", "c4_like"])
 def test_fuse_v_mean_matches_reference_cuda_kernel(case):
     """smooth_v: V minus its channel mean through the fp16 accumulator, the mean added back in the
@@ -272,8 +312,10 @@ def test_errors_are_loud():
         sageattention.sageattn(q, k, v, pv_accum_dtype="fp64")
     with pytest.raises(ValueError):
         sageattention.sageattn(q, k, v[:, :, :32])
-    with pytest.raises(_capi.SageB200Error):
-        sageattention.core._sageattn_configured(q, k, v, "HND", False, "fp32", True, False, False, (128, 32, 32, 32))
+    with pytest.raises(_capi.SageB200Error):      # a grouping no kernel is built for: WARPK != BLKK
+        sageattention.core._sageattn_configured(q, k, v, "HND", False, "fp32", True, False, False, (128, 64, 32, 32))
+    with pytest.raises(_capi.SageB200Error):      # 32-key scale blocks with the fp8 P.V variant
+        sageattention.core._sageattn_configured(q, k, v, "HND", False, "fp8", True, False, False, (128, 32, 32, 32))
 
 
 # ---------------------------------------------------------------------------------------------------
