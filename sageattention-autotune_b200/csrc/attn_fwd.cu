@@ -87,12 +87,8 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       which = 1;
     }
   } else if constexpr (PV_MODE == SAGE_B200_PV_F8) {
-    if constexpr (D == 256 || KSUB != 1) {
-      return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: the fp8 P.V mode is built for head_dim 64 and 128 and 64-key scale blocks only");
-    } else {
-      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
-      smem = v1::SmemPlan<D, true>::kDynamic;
-    }
+    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
+    smem = v1::SmemPlan<D, true>::kDynamic;
   } else {
     kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
     smem = v1::SmemPlan<D>::kDynamic;
@@ -170,12 +166,10 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
                "attn_fwd: per-thread k_scale must be 16-byte aligned (it is read four groups at a time)");
   if (head_dim != 64 && head_dim != 128 && head_dim != 256)
     return fail(SAGE_B200_ERR_INVALID, "attn_fwd: head_dim must be 64, 128 or 256 (pad first), got %d", head_dim);
-  if (head_dim == 256 && pv_accum == SAGE_B200_PV_F8)
-    return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: the fp8 P.V mode is built for head_dim 64 and 128 only");
   SAGE_REQUIRE(blk_q == 32 || blk_q == 64 || blk_q == 128, "attn_fwd: blk_q must be 32, 64 or 128");
   SAGE_REQUIRE(blk_k == 64 || blk_k == 32, "attn_fwd: blk_k must be 64 or 32, got %d", blk_k);
-  if (blk_k == 32 && (head_dim == 256 || pv_accum == SAGE_B200_PV_F8))
-    return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: 32-key scale blocks are built for head_dim 64 and 128 and the fp16-V modes");
+  if (blk_k == 32 && head_dim == 256)
+    return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: 32-key scale blocks are built for head_dim 64 and 128");
   if (granularity == SAGE_B200_GRAN_PER_THREAD) {
     SAGE_REQUIRE(warp_q >= 8 && warp_q <= blk_q && (warp_q & (warp_q - 1)) == 0, "attn_fwd: bad warp_q %d", warp_q);
     if (warp_k != blk_k)
@@ -227,7 +221,7 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   rc = make_map(&mk, k, 1, batch, heads_kv, len_kv, head_dim, k_strides, box_qk, kStageRows, swz_qk, "k");
   if (rc) return rc;
   if (pv_accum == SAGE_B200_PV_F8)
-    rc = make_map(&mv, v, 1, batch, heads_kv, len_kv, head_dim, v_strides, head_dim, kStageRows, swz_qk, "v");
+    rc = make_map(&mv, v, 1, batch, heads_kv, len_kv, head_dim, v_strides, box_qk, kStageRows, swz_qk, "v");
   else
     rc = make_map(&mv, v, 2, batch, heads_kv, len_kv, head_dim, v_strides, 64, kStageRows, CU_TENSOR_MAP_SWIZZLE_128B, "v");
   if (rc) return rc;

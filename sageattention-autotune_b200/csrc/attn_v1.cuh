@@ -568,9 +568,10 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarVFull + vs), Plan::kVBytes);
 #pragma unroll
-        for (int pn = 0; pn < (kFp8 ? 1 : D / 64); ++pn)      // fp16: 64-channel panels; e4m3: one panel of D bytes
+        // fp16: 64-channel panels; e4m3: panels of up to 128 channels; either way 128 bytes per key and panel
+        for (int pn = 0; pn < (kFp8 ? (D > 128 ? D / 128 : 1) : D / 64); ++pn)
           ptx::tma_load_4d(smem_base + Plan::kVOff + vs * Plan::kVBytes + pn * (kBlockKV * 128), &tm_v,
-                           bars + 8 * (kBarVFull + vs), pn * 64, j * kBlockKV, h_kv, b);
+                           bars + 8 * (kBarVFull + vs), pn * (kFp8 ? 128 : 64), j * kBlockKV, h_kv, b);
       }
       if (!ok) {
         // leave no copy in flight behind us: wait (bounded by the hardware try_wait) for what was issued
@@ -600,7 +601,8 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // carries out of the field for shared-memory addresses: build them once, then add offsets.
       const uint64_t q_desc0 = desc_kmajor<kRowBytesQK>(q_smem);
       const uint64_t k_desc0 = desc_kmajor<kRowBytesQK>(k_smem);
-      const uint64_t v_desc0 = kFp8 ? desc_mnmajor_f8<D>(v_smem) : desc_mnmajor(v_smem, kBlockKV * 128);
+      const uint64_t v_desc0 = (kFp8 && D <= 128) ? desc_mnmajor_f8<(D <= 128 ? D : 128)>(v_smem)
+                                                  : desc_mnmajor(v_smem, kBlockKV * 128);
 
       auto issue_qk = [&](int t, int stage) {
         const uint32_t d_t = tmem_base + t * 256;
@@ -626,7 +628,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           if constexpr (kFp8) {
 #pragma unroll
             for (int s = 0; s < kBlockKV / 32; ++s)   // 32 keys per instruction: 8 columns of P, 32 rows of V
-              ptx::mma_f8_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 32 * D) >> 4), idp,
+              ptx::mma_f8_ts(d_t, a_t + s * 8, db0 + static_cast<uint64_t>((s * 32 * (D > 128 ? 128 : D)) >> 4), idp,
                              (accumulate || s != 0) ? 1u : 0u);
           } else {
 #pragma unroll

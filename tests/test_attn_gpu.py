@@ -314,8 +314,9 @@ def test_errors_are_loud():
         sageattention.sageattn(q, k, v[:, :, :32])
     with pytest.raises(_capi.SageB200Error):      # a grouping no kernel is built for: WARPK != BLKK
         sageattention.core._sageattn_configured(q, k, v, "HND", False, "fp32", True, False, False, (128, 64, 32, 32))
-    with pytest.raises(_capi.SageB200Error):      # 32-key scale blocks with the fp8 P.V variant
-        sageattention.core._sageattn_configured(q, k, v, "HND", False, "fp8", True, False, False, (128, 32, 32, 32))
+    q2, k2, v2 = make_qkv(1, 2, 2, 64, 256, torch.float16, "HND", seed=2)
+    with pytest.raises(_capi.SageB200Error):      # 32-key scale blocks at head_dim 256
+        sageattention.core._sageattn_configured(q2, k2, v2, "HND", False, "fp32", True, False, False, (128, 32, 32, 32))
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -336,25 +337,27 @@ def test_quant_v_fp8_matches_oracle_bit_for_bit():
 
 
 @pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("D,dtype,layout,N", [(128, torch.bfloat16, "HND", 1000), (64, torch.float16, "NHD", 512),
-                                              (128, torch.float16, "HND", 2320)])
-def test_fp8_core_matches_oracle(D, dtype, layout, N, causal):
+@pytest.mark.parametrize("D,dtype,layout,N,cfg", [(128, torch.bfloat16, "HND", 1000, CFG), (64, torch.float16, "NHD", 512, CFG),
+                                                  (128, torch.float16, "HND", 2320, CFG),
+                                                  (256, torch.bfloat16, "NHD", 900, CFG),
+                                                  (128, torch.float16, "HND", 700, (128, 32, 32, 32))])
+def test_fp8_core_matches_oracle(D, dtype, layout, N, cfg, causal):
     from sageattention import quant
     from sageattention.core import attn_fwd_quantized
     cuda_or_fail()
     q, k, v = make_qkv(1, 4, 2, N, D, dtype, layout, seed=N + D, k_bias=2.0)
     km = quant.mean_k(k, layout)
-    q8, qs, k8, ks = quant.per_thread_int8(q, k, km, tensor_layout=layout, div="ieee")
+    q8, qs, k8, ks = quant.per_thread_int8(q, k, km, cfg[0], cfg[2], cfg[1], cfg[3], tensor_layout=layout, div="ieee")
     vq, vs = quant.quant_v_fp8(v, layout)
     out = torch.empty_like(q)
-    lse = attn_fwd_quantized(q8, k8, vq, out, qs, ks, layout, causal, D ** -0.5, CFG, "fp32", True, "per_thread", vs)
+    lse = attn_fwd_quantized(q8, k8, vq, out, qs, ks, layout, causal, D ** -0.5, cfg, "fp32", True, "per_thread", vs)
     torch.cuda.synchronize()
     exp, exp_lse = O.attend_fp8(q8.cpu(), k8.cpu(), vq.cpu(), vs.cpu(), qs.cpu(), ks.cpu(), layout, causal,
-                                out_dtype=dtype, return_lse=True)
+                                BLKQ=cfg[0], WARPQ=cfg[2], BLKK=cfg[1], WARPK=cfg[3], out_dtype=dtype, return_lse=True)
     # e4m3 keeps 3 mantissa bits: where the kernel's 2^x and the emulation's differ in the last place, P
     # can round to neighbouring e4m3 values 6-12 % apart, which early causal rows (few keys) do not
     # average out - hence the wider max-abs bound for this variant; the cosine bound is unchanged
-    _assert_close(out, exp, ("fp8", D, dtype, layout, N, causal), max_abs=5e-2)
+    _assert_close(out, exp, ("fp8", D, dtype, layout, N, cfg, causal), max_abs=5e-2)
     assert float((lse.cpu() - exp_lse).abs().max()) <= 2e-2
 
 
