@@ -164,7 +164,7 @@ int sage_b200_smooth_v_f16(const void* v, const void* v_mean, void* out, int dty
  *              non-zero code there if one of its bounded waits ran out
  *   causal     top-left aligned: key j is visible to query i iff j <= i
  *   head_dim   64, 128 or 256 (the reference's dispatch, csrc/dispatch_utils.h:34-47)
- *   blk_k, warp_k  64 or 32, warp_k = blk_k (32 not at head_dim 256)
+ *   blk_k, warp_k  64 or 32, warp_k = blk_k
  * The same inputs give the same bits on every call.
  */
 int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* out,

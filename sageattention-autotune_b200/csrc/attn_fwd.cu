@@ -168,8 +168,6 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
     return fail(SAGE_B200_ERR_INVALID, "attn_fwd: head_dim must be 64, 128 or 256 (pad first), got %d", head_dim);
   SAGE_REQUIRE(blk_q == 32 || blk_q == 64 || blk_q == 128, "attn_fwd: blk_q must be 32, 64 or 128");
   SAGE_REQUIRE(blk_k == 64 || blk_k == 32, "attn_fwd: blk_k must be 64 or 32, got %d", blk_k);
-  if (blk_k == 32 && head_dim == 256)
-    return fail(SAGE_B200_ERR_UNSUPPORTED, "attn_fwd: 32-key scale blocks are built for head_dim 64 and 128");
   if (granularity == SAGE_B200_GRAN_PER_THREAD) {
     SAGE_REQUIRE(warp_q >= 8 && warp_q <= blk_q && (warp_q & (warp_q - 1)) == 0, "attn_fwd: bad warp_q %d", warp_q);
     if (warp_k != blk_k)
@@ -230,6 +228,7 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   const dim3 grid((len_q + rows_per_cta - 1) / rows_per_cta, heads_q, batch);
   if (blk_k == 32) {
     if (head_dim == 64) return launch_attn_mode<64, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+    if (head_dim == 256) return launch_attn_mode<256, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
     return launch_attn_mode<128, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
   }
   if (head_dim == 64) return launch_attn_mode<64, 1>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);

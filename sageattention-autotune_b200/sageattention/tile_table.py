@@ -19,8 +19,7 @@ QK_CONFIGS = (
 )
 DEFAULT_QK_CONFIG = QK_CONFIGS[0]
 
-# groupings the sm_100a attention kernels consume: BLKK = WARPK = 64 or 32, i.e. all four (with 32-key
-# blocks not for head_dim 256 or the fp8 P.V variant)
+# groupings the sm_100a attention kernels consume: BLKK = WARPK = 64 or 32, i.e. all four
 SUPPORTED_QK_CONFIGS = tuple(c for c in QK_CONFIGS if c[1] == c[3] and c[1] in (32, 64))
 
 _SEQ_BUCKETS = (1024, 4096, 16384, 65536)
