@@ -102,7 +102,7 @@ int sage_b200_mean_k_static(const void* k, void* km, int dtype, int batch, int h
  *   scale    fp32 (batch, heads, groups) contiguous with
  *            groups = ceil(len/blk) * (blk/warp) * {8 | 4}   for the two per-thread kinds,
  *            groups = ceil(len/blk)                           for SAGE_B200_GROUP_BLOCK
- *   blk      BLKQ or BLKK of the attention tile config (32, 64 or 128)
+ *   blk      BLKQ or BLKK of the attention tile config (16, 32, 64 or 128; 16 serves per-warp Q scales with WARPQ = 16)
  *   warp     WARPQ or WARPK (8..blk, a power of two); ignored for SAGE_B200_GROUP_BLOCK
  * Rows past `len` inside the last block behave like the reference's masked loads:
  * they read as 0, the mean is still subtracted from them, they enter the maximum and

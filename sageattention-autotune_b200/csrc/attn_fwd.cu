@@ -166,7 +166,7 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
                "attn_fwd: per-thread k_scale must be 16-byte aligned (it is read four groups at a time)");
   if (head_dim != 64 && head_dim != 128 && head_dim != 256)
     return fail(SAGE_B200_ERR_INVALID, "attn_fwd: head_dim must be 64, 128 or 256 (pad first), got %d", head_dim);
-  SAGE_REQUIRE(blk_q == 32 || blk_q == 64 || blk_q == 128, "attn_fwd: blk_q must be 32, 64 or 128");
+  SAGE_REQUIRE(blk_q == 16 || blk_q == 32 || blk_q == 64 || blk_q == 128, "attn_fwd: blk_q must be 16, 32, 64 or 128");
   SAGE_REQUIRE(blk_k == 64 || blk_k == 32, "attn_fwd: blk_k must be 64 or 32, got %d", blk_k);
   if (granularity == SAGE_B200_GRAN_PER_THREAD) {
     SAGE_REQUIRE(warp_q >= 8 && warp_q <= blk_q && (warp_q & (warp_q - 1)) == 0, "attn_fwd: bad warp_q %d", warp_q);

@@ -407,6 +407,12 @@ def test_sageattn_per_warp_granularity(mode):
     ref, _ = O.sdpa_fp32(qc, kc, vc, "HND", True)
     c = O.compare(out.cpu(), ref)
     assert c["fro_rel"] <= 0.02 and c["max_abs"] <= 0.1, c
+    # WARPQ = 16 (the reference's (128, 64, 16, 64) candidate): one Q scale per 16 rows
+    from sageattention.core import _sageattn_configured
+    out16 = _sageattn_configured(q, k, v, "HND", True, mode, True, False, False, (128, 64, 16, 64), None, "per_warp")
+    q8, qs, k8, ks = O.quant_per_block(qc, kc, km, 16, 64, "HND")
+    exp16 = O.attend(q8, k8, vc, qs, ks, "HND", True, None, mode, "per_block", 16, 16, 64, 64, torch.float16)
+    _assert_close(out16, exp16, ("per_warp 16", mode))
 
 
 @pytest.mark.parametrize("mode", ["fp32", "fp16+fp32", "fp16"])
