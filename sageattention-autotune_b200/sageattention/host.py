@@ -30,9 +30,11 @@ def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Option
     if hq % hkv:
         raise ValueError("num_qo_heads must be divisible by num_kv_heads")
     rep = hq // hkv
-    # 16 chunks: small enough that filling and draining the pipeline costs little, large enough that
-    # a chunk still fills the GPU (measured at 64 heads x 32768: 34.2 ms with 8 chunks, 33.1 with 16)
-    step = kv_heads_per_chunk or max(1, hkv // 16)
+    # 32 chunks: the copies in are the bound (29.1 ms for 64 heads x 32768 fp16, 30.0 ms with the copy out
+    # running against them), so what counts is how little is left after the last one lands: the last
+    # chunk's compute and copy out.  Measured for that case: 34.2 ms with 8 chunks, 32.6-33.1 with 16,
+    # 31.7 with 32 (two heads = 512 CTAs still fill the GPU), 33.8 with 64.
+    step = kv_heads_per_chunk or max(1, hkv // 32)
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
     main = torch.cuda.current_stream(device)

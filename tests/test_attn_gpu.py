@@ -501,3 +501,24 @@ def test_extreme_score_ranges(mode):
     _assert_close(out, exp, ("extreme", mode))
     assert float(((lse.cpu() - exp_lse).abs() / exp_lse.abs().clamp_min(1.0)).max()) <= 1e-3
 
+
+
+@pytest.mark.parametrize("layout,Hq,Hkv,chunk", [("HND", 12, 6, None), ("HND", 10, 5, 2), ("NHD", 8, 4, 3)])
+def test_host_buffer_entry_point_equals_the_device_call(layout, Hq, Hkv, chunk):
+    """sageattn_host (host tensors in, host tensor out, pipelined over groups of kv-heads) returns the
+    bits of one sageattn call on the whole tensors: heads are independent and the kernels are
+    deterministic, whatever the grouping (default, ragged last group, non-contiguous NHD slices).
+    (At this length the K mean adds its rows in the same order for any head count; for long sequences
+    the row split follows the number of heads in the call and the mean may move by one rounding.)"""
+    import sageattention
+    from sageattention.host import sageattn_host
+    cuda_or_fail()
+    q, k, v = make_qkv(2, Hq, Hkv, 1000, 128, torch.float16, layout, seed=77, k_bias=1.0, device="cpu")
+    q, k, v = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    got = sageattn_host(q, k, v, tensor_layout=layout, kv_heads_per_chunk=chunk, is_causal=True)
+    exp = sageattention.sageattn(q.cuda(), k.cuda(), v.cuda(), tensor_layout=layout, is_causal=True)
+    torch.cuda.synchronize()
+    assert not got.is_cuda and got.shape == q.shape and got.dtype == q.dtype
+    assert torch.equal(got, exp.cpu())
+    with pytest.raises(ValueError):
+        sageattn_host(q.cuda(), k, v)
