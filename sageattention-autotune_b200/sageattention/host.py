@@ -41,8 +41,12 @@ def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Option
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     pending = []
     with torch.cuda.device(device):
-        for lo in range(0, hkv, step):
-            hi = min(hkv, lo + step)
+        # the last group goes head by head: whatever follows the last copy in is not overlapped
+        bounds = [(lo, min(hkv, lo + step)) for lo in range(0, hkv, step)]
+        if step > 1:
+            lo_last, hi_last = bounds.pop()
+            bounds += [(h, h + 1) for h in range(lo_last, hi_last)]
+        for lo, hi in bounds:
             with torch.cuda.stream(s_in):
                 dq = slice_heads(q, tensor_layout, lo * rep, hi * rep).to(device, non_blocking=True)
                 dk = slice_heads(k, tensor_layout, lo, hi).to(device, non_blocking=True)
