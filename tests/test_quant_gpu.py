@@ -113,6 +113,23 @@ def test_mean_k_within_one_ulp_of_torch(D, dtype, layout, N):
     assert float((a != b).float().mean()) < 0.05
 
 
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+def test_mean_k_does_not_depend_on_the_grouping_of_heads(layout):
+    """A (batch, head) plane's mean has the same bits whether it is reduced with the whole tensor or
+    alone (a head group of the pipelined host call, a rank's shard of the heads): the row split
+    follows the sequence length only.  Long enough for many splits per plane."""
+    from sageattention import quant
+    cuda_or_fail()
+    _, k, _ = make_qkv(2, 6, 6, 20000, 128, torch.bfloat16, layout, seed=17, k_bias=2.0)
+    full = quant.mean_k(k, layout)
+    hdim = 1 if layout == "HND" else 2
+    for lo, hi in ((0, 1), (1, 4), (4, 6)):
+        part = quant.mean_k(k.narrow(hdim, lo, hi - lo), layout)
+        assert torch.equal(part, full.narrow(hdim, lo, hi - lo)), (layout, lo, hi)
+    one = quant.mean_k(k[1:2].narrow(hdim, 5, 1), layout)
+    assert torch.equal(one, full[1:2].narrow(hdim, 5, 1))
+
+
 def test_cast_v_is_exactly_torch_cast():
     from sageattention import quant
     cuda_or_fail()
