@@ -160,8 +160,12 @@ int sage_b200_smooth_v_f16(const void* v, const void* v_mean, void* out, int dty
  *              out as sage_b200_quant_int8 writes them for (blk_q, warp_q) / (blk_k, warp_k)
  *   lse        NULL, or fp32 (batch, heads_q, len_q): log2(sum) + max in base 2, as the
  *              reference kernel defines it (qk_int8_sv_f16_kernel_sm80.cuh:645-656)
- *   status     NULL, or 4 int32 on the device, zeroed by the caller; the kernel writes a
- *              non-zero code there if one of its bounded waits ran out
+ *   status     NULL, or 4 int32 the GPU can write (device memory, or pinned host memory, which a
+ *              host can poll without synchronising), zeroed by the caller; if one of the kernel's
+ *              bounded waits runs out, the first CTA to give up writes {code, blockIdx.x, .y, .z}
+ *              there (code 10-69 = the wait that ran out, 99 = a CTA that started after another one
+ *              had given up).  With or without a status word a CTA that gives up fills its rows of
+ *              `out` with NaN, and the remaining CTAs of that launch return at once
  *   causal     top-left aligned: key j is visible to query i iff j <= i
  *   head_dim   64, 128 or 256 (the reference's dispatch, csrc/dispatch_utils.h:34-47)
  *   blk_k, warp_k  64 or 32, warp_k = blk_k
@@ -174,6 +178,15 @@ int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* ou
                        const int64_t v_strides[3], const int64_t o_strides[3], int is_causal,
                        float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k,
                        int granularity, int pv_accum, void* stream);
+
+/*
+ * Budget of every bounded wait inside the attention kernels, in SM clocks, for launches made after
+ * the call (process-wide; the default, about two seconds, is restored by a value <= 0).  Returns the
+ * previous budget.  The reference has nothing comparable (its launcher does not even check the
+ * launch, csrc/qattn/qk_int8_sv_f16_launch_sm80.cuh:193-209); hosts with a watchdog shorter than two
+ * seconds lower it, and tests use a tiny value to drive the give-up path without faulting the GPU.
+ */
+long long sage_b200_set_wait_budget(long long cycles);
 
 /*
  * The same with fp16 accumulation of a smoothed V and the channel mean added back to the normalised

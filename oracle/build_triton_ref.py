@@ -36,7 +36,8 @@ def _load(path: str, name: str):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("SAGE_REFERENCE_DIR"), required="SAGE_REFERENCE_DIR" not in os.environ,
+                    help="checkout of woct0rdho/sageattention-autotune (or set SAGE_REFERENCE_DIR)")
     args = ap.parse_args()
     os.environ.pop("TRITON_INTERPRET", None)
 

@@ -1,10 +1,13 @@
-"""Builds libsage_b200.so (the C-ABI library declared in include/sage_b200.h) for sm_100a.
+"""Builds libsage_b200.so (the C-ABI library declared in include/sage_b200.h) for sm_100a, and
+libsage_b200_torch.so (the torch operators registered over it, csrc/torch_ops.cpp).
 
     python sageattention-autotune_b200/build.py [--force]
 
-Plain nvcc, no torch involved: the library depends on the CUDA runtime only and resolves the one
-driver entry point it needs (cuTensorMapEncodeTiled) at run time, so it loads on a machine without
-a GPU driver too.  Objects are cached under build/ and rebuilt when a source or header is newer.
+The C-ABI library is plain nvcc, no torch involved: it depends on the CUDA runtime only and resolves
+the one driver entry point it needs (cuTensorMapEncodeTiled) at run time, so it loads on a machine
+without a GPU driver too.  The operator library is one C++ file compiled with g++ against torch's
+stable-ABI headers; it links libsage_b200.so from its own directory.  Objects are cached under
+build/ and rebuilt when a source or header is newer.
 """
 from __future__ import annotations
 
@@ -18,6 +21,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "sageattention", "libsage_b200.so")
+TORCH_LIB = os.path.join(HERE, "sageattention", "libsage_b200_torch.so")
+CXX = os.environ.get("CXX", "g++")
 SOURCES = ["api.cu", "quant.cu", "attn_fwd.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -53,7 +58,28 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = [os.path.join(OBJ, s[:-3] + ".o") for s in SOURCES]
     if jobs or not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
         run([NVCC, "-shared", "-o", LIB, *objs, "-cudart", "shared"])
+    build_torch_ops(force)
     return LIB
+
+
+def build_torch_ops(force: bool = False) -> str:
+    """g++ on csrc/torch_ops.cpp: stable-ABI headers of the installed torch (target version 2.10, the
+    first with the tensor-creation calls used), linked against libsage_b200.so beside it ($ORIGIN)."""
+    import torch
+    src = os.path.join(CSRC, "torch_ops.cpp")
+    hdr = os.path.join(HERE, "..", "include", "sage_b200.h")
+    if not force and os.path.exists(TORCH_LIB) and \
+            os.path.getmtime(TORCH_LIB) >= max(os.path.getmtime(src), os.path.getmtime(hdr), os.path.getmtime(LIB)):
+        return TORCH_LIB
+    tdir = os.path.dirname(torch.__file__)
+    cmd = [CXX, "-std=c++20", "-O2", "-fPIC", "-shared", "-DUSE_CUDA", "-DTORCH_TARGET_VERSION=0x020a000000000000",
+           f"-I{tdir}/include", "-I/usr/local/cuda/include", src, "-o", TORCH_LIB,
+           f"-L{os.path.dirname(LIB)}", "-l:libsage_b200.so", f"-L{tdir}/lib", "-ltorch", "-ltorch_cpu", "-lc10",
+           "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    return TORCH_LIB
 
 
 if __name__ == "__main__":

@@ -1,5 +1,5 @@
-// Shared pieces of the attention kernels: launch parameters, bounded mbarrier waits, UMMA
-// descriptors and the optional debug trace.
+// Shared pieces of the attention kernels: launch parameters, bounded mbarrier waits, the abort
+// protocol and UMMA descriptors.
 #pragma once
 
 #include <cuda.h>
@@ -14,7 +14,7 @@ constexpr int kBlockKV = 128;
 constexpr int kAttnThreads = 384;
 constexpr int kKStages = 3;
 constexpr int kVStages = 3;
-constexpr long long kWaitCycles = 4000000000LL;   // about two seconds of SM clock
+constexpr long long kWaitCycles = 4000000000LL;   // default wait budget: about two seconds of SM clock
 constexpr float kLog2e = 1.44269504088896340736f;
 constexpr float kMagicF = 12582912.0f;            // 1.5 * 2^23
 constexpr uint32_t kMagicI = 0x4B400000u;
@@ -35,47 +35,59 @@ struct AttnParams {
   int causal;
   float scale_log2;              // sm_scale * log2(e)
   int64_t os_b, os_h, os_n;
-  unsigned long long launch_id;  // non-zero, unique per launch of this process (see g_attn_abort_id)
-#ifdef SAGE_TRACE
-  long long* trace;              // debug builds only: per-role event timestamps of one CTA
-#endif
+  unsigned long long launch_id;  // non-zero, unique per launch of this process (see g_attn_abort)
+  long long wait_cycles;         // budget of every bounded wait, in SM clocks
 };
 
-// Identifier of the last launch in which a bounded wait ran out.  A CTA that starts after that
-// returns at once, so a launch whose pipeline is stuck ends after one wait period instead of one
-// period per wave of CTAs, whether or not the caller passed a status word.
-static __device__ unsigned long long g_attn_abort_id = 0;
+// Abort protocol.  When a bounded wait runs out, the CTA records {launch id, wall time} in a device
+// word pair; CTAs of the same launch that start later see it and return at once, so a launch whose
+// pipeline is stuck ends after one wait period instead of one period per wave of CTAs, whether or not
+// the caller passed a status word.  The record expires after kAbortHoldNs: a launch id that is baked
+// into a captured graph is therefore not condemned for good, a later replay runs normally.
+struct AbortRecord {
+  unsigned long long id;
+  unsigned long long when_ns;
+};
+static __device__ AbortRecord g_attn_abort = {0ull, 0ull};
+constexpr unsigned long long kAbortHoldNs = 5000000000ull;
 
-__device__ __forceinline__ bool launch_aborted(const AttnParams& p) {
-  if (*reinterpret_cast<volatile unsigned long long*>(&g_attn_abort_id) == p.launch_id) return true;
-  return p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0;
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
+__device__ __forceinline__ bool launch_aborted(const AttnParams& p) {
+  const volatile AbortRecord* r = &g_attn_abort;
+  if (r->id != p.launch_id) return false;
+  return global_ns() - r->when_ns < kAbortHoldNs;
+}
+// `code` names the wait that ran out (or kCodeLateCta for a CTA that found the launch already aborted)
+constexpr int kCodeLateCta = 99;
 __device__ __forceinline__ void publish_abort(const AttnParams& p, int code) {
-  *reinterpret_cast<volatile unsigned long long*>(&g_attn_abort_id) = p.launch_id;
-  if (p.status != nullptr && atomicCAS(p.status, 0, code) == 0) {
+  if (code != kCodeLateCta) {
+    volatile AbortRecord* r = &g_attn_abort;
+    r->when_ns = global_ns();
+    __threadfence();
+    r->id = p.launch_id;
+  }
+  if (p.status != nullptr && atomicCAS_system(p.status, 0, code) == 0) {
     p.status[1] = blockIdx.x;
     p.status[2] = blockIdx.y;
     p.status[3] = blockIdx.z;
+    __threadfence_system();
   }
 }
-
-#ifdef SAGE_TRACE
-// role r writes (event << 56 | j << 40 | clock) into trace[r * 8192 + n]; slot 0 holds n
-#define SAGE_TR(role, ev, j)                                                                         \
-  do {                                                                                               \
-    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {               \
-      long long* base_ = p.trace + (role) * 8192;                                                    \
-      long long n_ = base_[0];                                                                       \
-      if (n_ < 8190) {                                                                               \
-        base_[1 + n_] = (static_cast<long long>(ev) << 56) | (static_cast<long long>(j) << 40) |     \
-                        (clock64() & 0xffffffffffLL);                                                \
-        base_[0] = n_ + 1;                                                                           \
-      }                                                                                              \
-    }                                                                                                \
-  } while (0)
-#else
-#define SAGE_TR(role, ev, j) do {} while (0)
-#endif
+// A CTA that gives up leaves no stale data behind: its rows of the output read as NaN.
+__device__ __forceinline__ void poison_rows(const AttnParams& p, int rows, int q0, int b, int h, int head_dim) {
+  for (int i = threadIdx.x; i < rows * (head_dim / 8); i += blockDim.x) {
+    const int r = q0 + i / (head_dim / 8);
+    if (r < p.len_q) {
+      unsigned short* orow = static_cast<unsigned short*>(p.out) + b * p.os_b + h * p.os_h + r * p.os_n;
+      *reinterpret_cast<uint4*>(orow + (i % (head_dim / 8)) * 8) =
+          make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu);
+    }
+  }
+}
 
 // packed add of two values of the output type (reference: __hadd2 on DTypeOut2,
 // csrc/qattn/qk_int8_sv_f16_kernel_sm80.cuh:551-569)
@@ -90,25 +102,42 @@ __device__ __forceinline__ uint32_t add2_out(uint32_t a, uint32_t b) {
   }
 }
 
-// Bounded mbarrier wait.  Returns false if the CTA is aborting.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
+// Bounded mbarrier wait.  Returns false if the CTA is aborting.  A waiting thread should cost the
+// scheduler nothing: after one plain try the loop uses the form of try_wait that lets the hardware
+// suspend the thread for up to kSuspendNs per attempt, and looks at the abort flag and the clock only
+// between attempts, so a warp that waits a whole block time issues a handful of instructions.
+#ifndef SAGE_WAIT_HINT_NS
+#define SAGE_WAIT_HINT_NS 2000
+#endif
+constexpr uint32_t kSuspendNs = SAGE_WAIT_HINT_NS;
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                         long long budget) {
+  if (ptx::mbar_test_wait(bar, parity)) return true;       // the common case: the phase has completed
   const long long t0 = clock64();
   for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i)
-      if (ptx::mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > budget) {
       atomicCAS(const_cast<int*>(abort_flag), 0, code);
       return false;
     }
+    if (kSuspendNs != 0 ? ptx::mbar_try_wait_suspend(bar, parity, kSuspendNs) : ptx::mbar_try_wait(bar, parity))
+      return true;
   }
 }
 
 // Same, for code that goes on to warp-collective tcgen05.ld/st: the verdict is made warp-uniform.
-__device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, code));
+__device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                              long long budget) {
+  return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, code, budget));
+}
+
+// For the teardown of an aborting CTA: wait, with a fixed number of attempts, for a bulk copy that was
+// already issued to land (its barrier phase to complete).  Shared memory must not receive data after
+// the CTA has exited.
+__device__ __forceinline__ bool drain_bar(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < 200000; ++i)
+    if (ptx::mbar_try_wait_suspend(bar, parity, 1000u)) return true;
+  return false;
 }
 
 // K-major operand tile whose rows are ROW_BYTES wide (64 -> 64-byte swizzle, 128 -> 128-byte swizzle)

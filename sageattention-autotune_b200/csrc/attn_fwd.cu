@@ -135,10 +135,12 @@ static int launch_attn_mode(int pv_accum, int out_dtype, const CUtensorMap& mq, 
 
 using namespace sage;
 
-#ifdef SAGE_TRACE
-static long long* g_trace = nullptr;
-extern "C" void sage_b200_set_trace(long long* ptr) { g_trace = ptr; }
-#endif
+// budget of the kernels' bounded waits, in SM clocks (see sage_b200_set_wait_budget)
+static std::atomic<long long> g_wait_cycles{kWaitCycles};
+
+extern "C" long long sage_b200_set_wait_budget(long long cycles) {
+  return g_wait_cycles.exchange(cycles > 0 ? cycles : kWaitCycles, std::memory_order_relaxed);
+}
 
 static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const float* v_scale, const void* v_mean, void* out,
                                   const float* q_scale, const float* k_scale, float* lse, int32_t* status,
@@ -206,9 +208,7 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   p.os_b = o_strides[0];
   p.os_h = o_strides[1];
   p.os_n = o_strides[2];
-#ifdef SAGE_TRACE
-  p.trace = g_trace;
-#endif
+  p.wait_cycles = g_wait_cycles.load(std::memory_order_relaxed);
 
   constexpr int kStageRows = 128;   // keys per TMA stage in both kernels
   CUtensorMap mq, mk, mv;

@@ -138,11 +138,9 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 #pragma unroll
     for (int t = 0; t < kNA; ++t) a[t] = p.scale_log2 * (q_sc * a[t]);
 
-    if (row == 0) SAGE_TR(tile, 1, j);
-    ok = wait_bar_warp(bar_s_full, j & 1, abort_flag, 10 + tile);
+    ok = wait_bar_warp(bar_s_full, j & 1, abort_flag, 10 + tile, p.wait_cycles);
     if (!ok) break;
     ptx::tc_fence_after();
-    if (row == 0) SAGE_TR(tile, 2, j);
 
     uint32_t s[128];
     ptx::tmem_ld32<0>(t_s + 0, s);
@@ -150,7 +148,6 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     ptx::tmem_ld32<64>(t_s + 64, s);
     ptx::tmem_ld32<96>(t_s + 96, s);
     ptx::tmem_wait_ld();
-    if (row == 0) SAGE_TR(tile, 3, j);
 
     const bool need_mask = (k0 + kBlockKV > p.len_kv) || (p.causal && (k0 + kBlockKV - 1 > q_row0));
     float m_blk = -INFINITY;
@@ -226,7 +223,7 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 
     if constexpr (!kInstBuf) {
       if (j > 0 && __any_sync(0xffffffffu, rescale)) {
-        ok = wait_bar_warp(bar_pv_done, (j - 1) & 1, abort_flag, 20 + tile);
+        ok = wait_bar_warp(bar_pv_done, (j - 1) & 1, abort_flag, 20 + tile, p.wait_cycles);
         if (!ok) break;
         ptx::tc_fence_after();
         if constexpr (kF16Acc) {
@@ -260,7 +257,6 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       }
     }
 
-    if (row == 0) SAGE_TR(tile, 4, j);
     // P = 2^(S*a - m), packed to fp16 pairs in place
     float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
     // Of every kPolyDen groups of four columns, kPolyNum evaluate 2^x with a polynomial on the FMA pipe
@@ -345,13 +341,11 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     }
     d_sum = d_sum * alpha + ((sum0 + sum1) + (sum2 + sum3));
 
-    if (row == 0) SAGE_TR(tile, 5, j);
     ptx::tmem_st32<0>(t_p + 0, s);
     if constexpr (!kFp8) ptx::tmem_st32<32>(t_p + 32, s);     // e4m3: four keys per column, 32 columns
     ptx::tmem_wait_st();
     ptx::tc_fence_before();
     ptx::mbar_arrive(bar_p_full);
-    if (row == 0) SAGE_TR(tile, 6, j);
 
     if constexpr (kInstBuf) {
       // "fp16+fp32": this block's P.V is accumulated in fp16 from zero, 64 channels at a time, and
@@ -359,7 +353,7 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
       const bool any_rescale = __any_sync(0xffffffffu, rescale);
 #pragma unroll 1
       for (int ch = 0; ch < D / 64 && ok; ++ch) {
-        ok = wait_bar_warp(bar_pv_done, (j * (D / 64) + ch) & 1, abort_flag, 30 + tile);
+        ok = wait_bar_warp(bar_pv_done, (j * (D / 64) + ch) & 1, abort_flag, 30 + tile, p.wait_cycles);
         if (!ok) break;
         ptx::tc_fence_after();
 #pragma unroll
@@ -387,7 +381,7 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 
   if (ok && n_blocks > 0) {
     if constexpr (!kInstBuf) {
-      ok = wait_bar_warp(bar_pv_done, (n_blocks - 1) & 1, abort_flag, 40 + tile);
+      ok = wait_bar_warp(bar_pv_done, (n_blocks - 1) & 1, abort_flag, 40 + tile, p.wait_cycles);
       if (ok) ptx::tc_fence_after();
     }
   }
@@ -489,9 +483,6 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int pair = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
   const int q0 = pair * kTiles * kTileQ;
 
-  // another CTA of this launch already gave up: do not queue more bounded waits behind it
-  if (launch_aborted(p)) return;
-
   int n_blk[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -518,7 +509,9 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       ptx::mbar_init(bars + 8 * (kBarSFree + t), kTileQ);
     }
     ptx::mbar_init(bars + 8 * kBarDrain, 1);
-    *abort_flag = 0;
+    // another CTA of this launch already gave up: do not queue more bounded waits behind it.  One thread
+    // decides for the whole CTA, and every thread reads the verdict after the barrier below.
+    *abort_flag = launch_aborted(p) ? kCodeLateCta : 0;
     ptx::fence_barrier_init();
   }
   if (warp == 8) {
@@ -529,8 +522,11 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool late = (*abort_flag != 0);
 
-  if (warp < 8) {
+  if (late) {
+    // nothing was issued: fall through to the teardown
+  } else if (warp < 8) {
     ptx::reg_inc<232>();
     const int tile = warp >> 2;
     softmax_role<D, PV_MODE, OUT_DTYPE, KSUB>(p, bars, tmem_base, abort_flag, tile, threadIdx.x & 127, n_blk[tile],
@@ -554,17 +550,19 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           ptx::tma_load_4d(q_smem + t * Plan::kQBytes + pn * (kTileQ * kPanelBytesQK), &tm_q, bars + 8 * kBarQFull,
                            pn * kPanelBytesQK, q0 + t * kTileQ, h, b);
       bool ok = true;
+      int j_k = 0, j_v = 0;      // blocks whose K / V copy was issued
 #pragma unroll 1
       for (int j = 0; j < n_max && ok; ++j) {
         const int ks = j % kStK, vs = j % kStV;
-        ok = wait_bar(bars + 8 * (kBarKEmpty + ks), ((j / kStK) & 1) ^ 1, abort_flag, 50);
+        ok = wait_bar(bars + 8 * (kBarKEmpty + ks), ((j / kStK) & 1) ^ 1, abort_flag, 50, p.wait_cycles);
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarKFull + ks), Plan::kKBytes);
 #pragma unroll
         for (int pn = 0; pn < kPanelsQKLoad; ++pn)
           ptx::tma_load_4d(smem_base + Plan::kKOff + ks * Plan::kKBytes + pn * (kBlockKV * kPanelBytesQK), &tm_k,
                            bars + 8 * (kBarKFull + ks), pn * kPanelBytesQK, j * kBlockKV, h_kv, b);
-        ok = wait_bar(bars + 8 * (kBarVEmpty + vs), ((j / kStV) & 1) ^ 1, abort_flag, 51);
+        j_k = j + 1;
+        ok = wait_bar(bars + 8 * (kBarVEmpty + vs), ((j / kStV) & 1) ^ 1, abort_flag, 51, p.wait_cycles);
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarVFull + vs), Plan::kVBytes);
 #pragma unroll
@@ -572,13 +570,14 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int pn = 0; pn < (kFp8 ? (D > 128 ? D / 128 : 1) : D / 64); ++pn)
           ptx::tma_load_4d(smem_base + Plan::kVOff + vs * Plan::kVBytes + pn * (kBlockKV * 128), &tm_v,
                            bars + 8 * (kBarVFull + vs), pn * (kFp8 ? 128 : 64), j * kBlockKV, h_kv, b);
+        j_v = j + 1;
       }
-      if (!ok) {
-        // leave no copy in flight behind us: wait (bounded by the hardware try_wait) for what was issued
-        for (int s = 0; s < kStK; ++s)
-          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 0) &&
-                          !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 1); ++i) {}
-      }
+      // Leave no copy in flight behind us, whatever made the roles stop: wait (bounded) for Q and for the
+      // copies of the last stages' worth of blocks (earlier ones had landed before their stage was handed
+      // back).  After a normal run these phases completed long ago and every wait returns at once.
+      drain_bar(bars + 8 * kBarQFull, 0);
+      for (int j = max(0, j_k - kStK); j < j_k; ++j) drain_bar(bars + 8 * (kBarKFull + j % kStK), (j / kStK) & 1);
+      for (int j = max(0, j_v - kStV); j < j_v; ++j) drain_bar(bars + 8 * (kBarVFull + j % kStV), (j / kStV) & 1);
     } else if (warp == 9) {
       // ---------------- MMA issuer ----------------
       // The whole warp runs this loop and one elected lane issues: operands that are computed in
@@ -654,8 +653,8 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         __syncwarp();
       };
 
-      bool ok = wait_bar_warp(bars + 8 * kBarQFull, 0, abort_flag, 60);
-      if (ok && n_max > 0) ok = wait_bar_warp(bars + 8 * (kBarKFull + 0), 0, abort_flag, 61);
+      bool ok = wait_bar_warp(bars + 8 * kBarQFull, 0, abort_flag, 60, p.wait_cycles);
+      if (ok && n_max > 0) ok = wait_bar_warp(bars + 8 * (kBarKFull + 0), 0, abort_flag, 61, p.wait_cycles);
       if (ok && n_max > 0) {
         ptx::tc_fence_after();
         for (int t = 0; t < 2; ++t) {
@@ -671,27 +670,24 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int vs = j % kStV;
         const int nxt = j + 1;
         const int ks = nxt % kStK;
-        ok = wait_bar_warp(bars + 8 * (kBarVFull + vs), (j / kStV) & 1, abort_flag, 62);
+        ok = wait_bar_warp(bars + 8 * (kBarVFull + vs), (j / kStV) & 1, abort_flag, 62, p.wait_cycles);
         if (!ok) break;
         if (nxt < n_max) {
-          ok = wait_bar_warp(bars + 8 * (kBarKFull + ks), (nxt / kStK) & 1, abort_flag, 63);
+          ok = wait_bar_warp(bars + 8 * (kBarKFull + ks), (nxt / kStK) & 1, abort_flag, 63, p.wait_cycles);
           if (!ok) break;
         }
         if constexpr (!kInstBuf) {
           for (int t = 0; t < 2 && ok; ++t) {
             if (j < n_blk[t]) {
-              if (lane == 0) SAGE_TR(2, 10 + t, j);
-              ok = wait_bar_warp(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
+              ok = wait_bar_warp(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t, p.wait_cycles);
               if (!ok) break;
               ptx::tc_fence_after();
-              if (lane == 0) SAGE_TR(2, 12 + t, j);
               issue_pv(t, vs, j > 0);
               commit(bars + 8 * (kBarPvDone + t));
               if (nxt < n_blk[t]) {
                 issue_qk(t, ks);
                 commit(bars + 8 * (kBarSFull + t));
               }
-              if (lane == 0) SAGE_TR(2, 14 + t, j);
             }
           }
         } else {
@@ -699,8 +695,8 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           for (int ch = 0; ch < kChunks && ok; ++ch) {
             for (int t = 0; t < 2 && ok; ++t) {
               if (j < n_blk[t]) {
-                if (ch == 0) ok = wait_bar_warp(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t);
-                else ok = wait_bar_warp(bars + 8 * (kBarSFree + t), (j * kChunks + ch - 1) & 1, abort_flag, 66 + t);
+                if (ch == 0) ok = wait_bar_warp(bars + 8 * (kBarPFull + t), j & 1, abort_flag, 64 + t, p.wait_cycles);
+                else ok = wait_bar_warp(bars + 8 * (kBarSFree + t), (j * kChunks + ch - 1) & 1, abort_flag, 66 + t, p.wait_cycles);
                 if (!ok) break;
                 ptx::tc_fence_after();
                 issue_pv_chunk(t, vs, ch);
@@ -710,7 +706,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
           for (int t = 0; t < 2 && ok; ++t) {
             if (nxt < n_blk[t]) {
-              ok = wait_bar_warp(bars + 8 * (kBarSFree + t), (j * kChunks + kChunks - 1) & 1, abort_flag, 68 + t);
+              ok = wait_bar_warp(bars + 8 * (kBarSFree + t), (j * kChunks + kChunks - 1) & 1, abort_flag, 68 + t, p.wait_cycles);
               if (!ok) break;
               ptx::tc_fence_after();
               issue_qk(t, ks);
@@ -732,7 +728,10 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   if (warp == 8) ptx::tmem_dealloc(tmem_base, 512);
-  if (threadIdx.x == 0 && *abort_flag != 0) publish_abort(p, *abort_flag);
+  if (*abort_flag != 0) {
+    poison_rows(p, kTiles * kTileQ, q0, b, h, D);
+    if (threadIdx.x == 0) publish_abort(p, *abort_flag);
+  }
 }
 
 

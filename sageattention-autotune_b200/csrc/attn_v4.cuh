@@ -44,7 +44,7 @@ constexpr float kRefStep = 4.0f;
 constexpr int kScaleRing = 8;      // K dequantisation scales staged by the producer, one slot per block
 constexpr int kThreads = 512;
 // setmaxnreg is a warpgroup-wide instruction: the four warps of a group must ask for the same count
-constexpr int kRegsSoftmax = 144, kRegsFold = 184, kRegsIssue = 40;
+constexpr int kRegsSoftmax = 152, kRegsFold = 168, kRegsIssue = 40;
 static_assert(8 * kRegsSoftmax + 4 * kRegsFold + 4 * kRegsIssue <= 2048, "register file");
 
 enum BarIdx {
@@ -107,13 +107,6 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     q_sc = p.q_scale[(static_cast<int64_t>(b) * p.heads_q + h) * p.q_groups + g];
   }
 
-#ifdef SAGE_TRACE
-  long long tacc[4] = {0, 0, 0, 0};
-  long long tprev = clock64();
-#define V4_PH(k) do { const long long tn_ = clock64(); tacc[k] += tn_ - tprev; tprev = tn_; } while (0)
-#else
-#define V4_PH(k) do {} while (0)
-#endif
   float ref = -INFINITY;       // integer-valued reference exponent of this warpgroup's P and row sum
   float d_sum = 0.0f;          // row sum over this warpgroup's blocks, relative to `ref`
   bool ok = true;
@@ -123,11 +116,9 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     const int k0 = j * kBlockKV;
     const int buf = j % 3;
     const uint32_t t_s = tmem_base + lane_base + buf * 128;
-    V4_PH(0);
-    ok = wait_bar_warp(bars + 8 * (kBarSFull + buf), (j / 3) & 1, abort_flag, 10 + wg);
+    ok = wait_bar_warp(bars + 8 * (kBarSFull + buf), (j / 3) & 1, abort_flag, 10 + wg, p.wait_cycles);
     if (!ok) break;
     ptx::tc_fence_after();
-    V4_PH(1);
     // the eight dequantisation constants of this block, staged by the producer with the K tile
     float a[8];
     {
@@ -176,7 +167,6 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
         }
       }
     }
-    V4_PH(2);
 
     // new reference: integer, at least this block's maximum, never below anything already used, and
     // not below the other warpgroup's reference of block j-3.  That block's softmax finished before
@@ -265,18 +255,13 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     ptx::tmem_wait_st();
     ptx::tc_fence_before();
     ptx::mbar_arrive(bars + 8 * (kBarPFull + buf));       // also publishes ref_ring (release)
-    V4_PH(3);
   }
-#ifdef SAGE_TRACE
-  if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (row & 31) == 0)
-    for (int k = 0; k < 4; ++k) p.trace[(wg * 4 + (row >> 5)) * 8 + k] = tacc[k];
-#endif
 
   // combine the two warpgroups' row sums, hand 1/sum to the fold warps, write the LSE
   if (wg == 1) sum_xchg[row] = d_sum;                     // (its final reference is in ref_pub)
   ptx::mbar_arrive(bars + 8 * kBarSum);
   if (wg == 0) {
-    const bool got = wait_bar_warp(bars + 8 * kBarSum, 0, abort_flag, 14);
+    const bool got = wait_bar_warp(bars + 8 * kBarSum, 0, abort_flag, 14, p.wait_cycles);
     const float ref_b = ref_pub[kTileQ + row];
     const float r_fin = fmaxf(ref, ref_b);                // finite: block 0 has a visible key in every row
     const float total = d_sum * pow2_int(fmaxf(ref - r_fin, -127.0f)) +
@@ -302,18 +287,11 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
   for (int i = 0; i < D; ++i) o[i] = 0.0f;
   float r_out = -INFINITY;     // reference exponent O is expressed against
   bool ok = true;
-#ifdef SAGE_TRACE
-  long long facc[3] = {0, 0, 0};
-  long long fprev = clock64();
-#endif
 #pragma unroll 1
   for (int j = 0; j < n_blocks; ++j) {
-    ok = wait_bar_warp(bars + 8 * kBarTFull, j & 1, abort_flag, 30);
+    ok = wait_bar_warp(bars + 8 * kBarTFull, j & 1, abort_flag, 30, p.wait_cycles);
     if (!ok) break;
     ptx::tc_fence_after();
-#ifdef SAGE_TRACE
-    { const long long tn_ = clock64(); facc[0] += tn_ - fprev; fprev = tn_; }
-#endif
     const float r_blk = ref_ring[(j % kRefRing) * kTileQ + row];
     const float r_new = fmaxf(r_out, r_blk);
     // exact powers of two (the references are integers), and at most one of them differs from 1;
@@ -344,18 +322,8 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
     }
     ptx::tc_fence_before();
     ptx::mbar_arrive(bars + 8 * kBarTFree);
-#ifdef SAGE_TRACE
-    { const long long tn_ = clock64(); facc[1] += tn_ - fprev; fprev = tn_; facc[2] += plain ? 1 : 0; }
-#endif
   }
-#ifdef SAGE_TRACE
-  if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && row == 0) {
-    p.trace[80] = facc[0];
-    p.trace[81] = facc[1];
-    p.trace[82] = facc[2];
-  }
-#endif
-  if (ok) ok = wait_bar_warp(bars + 8 * kBarStats, 0, abort_flag, 40);
+  if (ok) ok = wait_bar_warp(bars + 8 * kBarStats, 0, abort_flag, 40, p.wait_cycles);
   if (ok && n_blocks > 0) {
     const int q_row = q_row0 + row;
     const float inv = inv_in[row];
@@ -399,20 +367,6 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int tile_idx = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
   const int q0 = tile_idx * kTileQ;
 
-  // another CTA of this launch already gave up: do not queue more bounded waits behind it
-  if (launch_aborted(p)) return;
-#ifdef SAGE_TRACE
-  // debug builds: clock and wall time of the first and the last CTA of the grid, to separate the SM
-  // clock from per-CTA overheads
-  const bool tr_cta = (blockIdx.y == 0 && blockIdx.z == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1));
-  if (p.trace != nullptr && tr_cta && threadIdx.x == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    p.trace[96 + (blockIdx.x == 0 ? 0 : 4)] = clock64();
-    p.trace[97 + (blockIdx.x == 0 ? 0 : 4)] = static_cast<long long>(gt);
-  }
-#endif
-
   const int kv_end = p.causal ? min(p.len_kv, q0 + kTileQ) : p.len_kv;
   const int n_blk = (kv_end + kBlockKV - 1) / kBlockKV;
 
@@ -435,7 +389,9 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     ptx::mbar_init(bars + 8 * kBarTFree, kTileQ);
     ptx::mbar_init(bars + 8 * kBarStats, kTileQ);
     ptx::mbar_init(bars + 8 * kBarDrain, 1);
-    *abort_flag = 0;
+    // another CTA of this launch already gave up: do not queue more bounded waits behind it.  One thread
+    // decides for the whole CTA, and every thread reads the verdict after the barrier below.
+    *abort_flag = launch_aborted(p) ? kCodeLateCta : 0;
     ptx::fence_barrier_init();
   }
   if (threadIdx.x < 2 * kTileQ) ref_pub[threadIdx.x] = -INFINITY;
@@ -447,8 +403,11 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool late = (*abort_flag != 0);
 
-  if (warp < 8) {
+  if (late) {
+    // nothing was issued: fall through to the teardown
+  } else if (warp < 8) {
     ptx::reg_inc<kRegsSoftmax>();
     softmax_role<D>(p, bars, tmem_base, abort_flag, ref_ring, inv_buf, ref_pub, sum_xchg, k_scales, warp >> 2,
                     threadIdx.x & 127, n_blk, q0, b, h);
@@ -491,10 +450,11 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       float4 sc_lo, sc_hi;
       load_scales(0, sc_lo, sc_hi);
       bool ok = true;
+      int j_k = 0, j_v = 0;
 #pragma unroll 1
       for (int j = 0; j < n_blk && ok; ++j) {
         const int ks = j % kKStages, vs = j % kVStages;
-        ok = wait_bar(bars + 8 * (kBarKEmpty + ks), ((j / kKStages) & 1) ^ 1, abort_flag, 50);
+        ok = wait_bar(bars + 8 * (kBarKEmpty + ks), ((j / kKStages) & 1) ^ 1, abort_flag, 50, p.wait_cycles);
         if (!ok) break;
         // this block's eight scales travel with the K tile: the arrive below releases the stores, and a
         // slot is reused kScaleRing blocks later, long after the softmax of this block has read it
@@ -507,20 +467,24 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarKFull + ks), Plan::kKBytes);
         ptx::tma_load_4d(smem_base + Plan::kKOff + ks * Plan::kKBytes, &tm_k, bars + 8 * (kBarKFull + ks), 0,
                          j * kBlockKV, h_kv, b);
-        ok = wait_bar(bars + 8 * (kBarVEmpty + vs), ((j / kVStages) & 1) ^ 1, abort_flag, 51);
+        j_k = j + 1;
+        ok = wait_bar(bars + 8 * (kBarVEmpty + vs), ((j / kVStages) & 1) ^ 1, abort_flag, 51, p.wait_cycles);
         if (!ok) break;
         ptx::mbar_arrive_expect_tx(bars + 8 * (kBarVFull + vs), Plan::kVBytes);
 #pragma unroll
         for (int pn = 0; pn < D / 64; ++pn)
           ptx::tma_load_4d(smem_base + Plan::kVOff + vs * Plan::kVBytes + pn * (kBlockKV * 128), &tm_v,
                            bars + 8 * (kBarVFull + vs), pn * 64, j * kBlockKV, h_kv, b);
+        j_v = j + 1;
       }
-      if (!ok) {
-        // leave no copy in flight behind us: wait (bounded) for what was issued
-        for (int s = 0; s < kKStages; ++s)
-          for (int i = 0; i < 4096 && !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 0) &&
-                          !ptx::mbar_try_wait(bars + 8 * (kBarKFull + s), 1); ++i) {}
-      }
+      // Leave no copy in flight behind us, whatever made the roles stop: wait (bounded) for Q and for the
+      // copies of the last stages' worth of blocks (earlier ones had landed before their stage was handed
+      // back).  After a normal run these phases completed long ago and every wait returns at once.
+      drain_bar(bars + 8 * kBarQFull, 0);
+      for (int j = max(0, j_k - kKStages); j < j_k; ++j)
+        drain_bar(bars + 8 * (kBarKFull + j % kKStages), (j / kKStages) & 1);
+      for (int j = max(0, j_v - kVStages); j < j_v; ++j)
+        drain_bar(bars + 8 * (kBarVFull + j % kVStages), (j / kVStages) & 1);
     } else if (warp == 13) {
       // ---------------- MMA issuer ----------------
       constexpr int kRowBytesQK = (D == 64) ? 64 : 128;
@@ -559,50 +523,33 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         __syncwarp();
       };
 
-      bool ok = wait_bar_warp(bars + 8 * kBarQFull, 0, abort_flag, 60);
+      bool ok = wait_bar_warp(bars + 8 * kBarQFull, 0, abort_flag, 60, p.wait_cycles);
       for (int blk = 0; blk < 3 && blk < n_blk && ok; ++blk) {
-        ok = wait_bar_warp(bars + 8 * (kBarKFull + blk % kKStages), 0, abort_flag, 61);
+        ok = wait_bar_warp(bars + 8 * (kBarKFull + blk % kKStages), 0, abort_flag, 61, p.wait_cycles);
         if (!ok) break;
         ptx::tc_fence_after();
         issue_qk(blk);
       }
-#ifdef SAGE_TRACE
-      long long macc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      long long mprev = clock64();
-#define V4_MPH(k) do { const long long tn_ = clock64(); macc[k] += tn_ - mprev; mprev = tn_; } while (0)
-#else
-#define V4_MPH(k) do {} while (0)
-#endif
 #pragma unroll 1
       for (int j = 0; j < n_blk && ok; ++j) {
-        V4_MPH(0);
-        ok = wait_bar_warp(bars + 8 * (kBarVFull + j % kVStages), (j / kVStages) & 1, abort_flag, 62);
+        ok = wait_bar_warp(bars + 8 * (kBarVFull + j % kVStages), (j / kVStages) & 1, abort_flag, 62, p.wait_cycles);
         if (!ok) break;
-        V4_MPH(1);
-        ok = wait_bar_warp(bars + 8 * (kBarPFull + j % 3), (j / 3) & 1, abort_flag, 64);
+        ok = wait_bar_warp(bars + 8 * (kBarPFull + j % 3), (j / 3) & 1, abort_flag, 64, p.wait_cycles);
         if (!ok) break;
-        V4_MPH(2);
         ptx::tc_fence_after();
-        V4_MPH(3);
         if (j >= 1) {                                // the previous block's T has been folded
-          ok = wait_bar_warp(bars + 8 * kBarTFree, (j - 1) & 1, abort_flag, 66);
+          ok = wait_bar_warp(bars + 8 * kBarTFree, (j - 1) & 1, abort_flag, 66, p.wait_cycles);
           if (!ok) break;
           ptx::tc_fence_after();
         }
         issue_pv(j);
-        V4_MPH(4);
         const int nxt = j + 3;                      // reuses the score buffer P(j) was read from
         if (nxt < n_blk) {
-          ok = wait_bar_warp(bars + 8 * (kBarKFull + nxt % kKStages), (nxt / kKStages) & 1, abort_flag, 63);
+          ok = wait_bar_warp(bars + 8 * (kBarKFull + nxt % kKStages), (nxt / kKStages) & 1, abort_flag, 63, p.wait_cycles);
           if (!ok) break;
           issue_qk(nxt);
         }
-        V4_MPH(5);
       }
-#ifdef SAGE_TRACE
-      if (p.trace != nullptr && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
-        for (int k = 0; k < 8; ++k) p.trace[64 + k] = macc[k];
-#endif
       // everything this warp issued must have retired before tensor memory is released
       if (ptx::elect_one()) ptx::tc_commit(bars + 8 * kBarDrain);
       __syncwarp();
@@ -614,15 +561,10 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   if (warp == 12) ptx::tmem_dealloc(tmem_base, 512);
-#ifdef SAGE_TRACE
-  if (p.trace != nullptr && tr_cta && threadIdx.x == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    p.trace[98 + (blockIdx.x == 0 ? 0 : 4)] = clock64();
-    p.trace[99 + (blockIdx.x == 0 ? 0 : 4)] = static_cast<long long>(gt);
+  if (*abort_flag != 0) {
+    poison_rows(p, kTileQ, q0, b, h, D);
+    if (threadIdx.x == 0) publish_abort(p, *abort_flag);
   }
-#endif
-  if (threadIdx.x == 0 && *abort_flag != 0) publish_abort(p, *abort_flag);
 }
 
 }  // namespace v4

@@ -11,7 +11,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libsage_b200.so")
+# SAGE_B200_LIB names another build of the same library (kernel experiments); normally unset
+_LIB_PATH = os.environ.get("SAGE_B200_LIB") or os.path.join(_HERE, "libsage_b200.so")
 
 F16, BF16 = 0, 1
 GROUP_Q_THREAD, GROUP_K_THREAD, GROUP_BLOCK = 0, 1, 2
@@ -25,7 +26,7 @@ EXPORTS = (
     "sage_b200_quant_int8", "sage_b200_smooth_quant_k_scratch_bytes", "sage_b200_smooth_quant_k",
     "sage_b200_cast_v_f16", "sage_b200_attn_fwd", "sage_b200_quant_v_fp8_scratch_bytes", "sage_b200_quant_v_fp8",
     "sage_b200_attn_fwd_fp8", "sage_b200_smooth_v_f16", "sage_b200_attn_fwd_fuse_v_mean",
-    "sage_b200_sageattn_workspace_bytes", "sage_b200_sageattn",
+    "sage_b200_sageattn_workspace_bytes", "sage_b200_sageattn", "sage_b200_set_wait_budget",
 )
 
 _lib = None
@@ -83,6 +84,8 @@ def lib() -> ctypes.CDLL:
         L.sage_b200_sageattn.restype = i
         L.sage_b200_sageattn.argtypes = [vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp, i, i, i, i, i, i, i,
                                          i64p, i64p, i64p, i64p, i, f, i, i, i, i, i, i, i, i, vp]
+        L.sage_b200_set_wait_budget.restype = ctypes.c_longlong
+        L.sage_b200_set_wait_budget.argtypes = [ctypes.c_longlong]
         _lib = L
     return _lib
 

@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _capi as C
+from . import ops as _ops          # loads the operator library and registers the fakes
 from . import quant as Q
 from .quant import cast_v_fp16, mean_k, per_block_int8, per_thread_int8
 from .tile_table import SUPPORTED_QK_CONFIGS, select_qk_config
@@ -55,6 +56,52 @@ class _Timed:
 
 def _check_status_enabled() -> bool:
     return os.getenv("SAGE_B200_CHECK", "0").lower() in ("1", "true", "yes", "on")
+
+
+# Device-side failures (a bounded wait inside the attention kernel ran out) are reported through a
+# status word.  Every launch gets one: four int32 per device in pinned host memory, which the GPU
+# writes through its mapped address and the host reads without synchronising.  The word is looked
+# at before the next launch on that device (so a failure surfaces one call late, never silently)
+# and by check_device_status(); with SAGE_B200_CHECK=1 every call synchronises and checks at once.
+_status_words = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(idx)
+    if word is None:
+        word = torch.zeros(4, dtype=torch.int32).pin_memory()
+        _status_words[idx] = word
+    return word
+
+
+def _raise_if_failed(word: torch.Tensor, when: str) -> None:
+    code = int(word[0])
+    if code != 0:
+        cta = tuple(int(x) for x in word[1:])
+        word.zero_()
+        raise C.SageB200Error(f"{when} attention launch gave up waiting (code {code}) in CTA {cta}; "
+                              "its output rows read as NaN")
+
+
+def check_device_status(device=None, synchronize: bool = True) -> None:
+    """Raise SageB200Error if an attention launch on `device` reported a failure since the last check."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if synchronize:
+        torch.cuda.synchronize(device)
+    _raise_if_failed(_status_word(device), "an earlier")
+
+
+def _launch_status(device: torch.device) -> torch.Tensor:
+    word = _status_word(device)
+    _raise_if_failed(word, "an earlier")
+    return word
+
+
+def _after_launch(device: torch.device, word: torch.Tensor) -> None:
+    if _check_status_enabled() and not torch.cuda.is_current_stream_capturing():
+        torch.cuda.synchronize(device)
+        _raise_if_failed(word, "the")
 
 
 def _padded_head_dim(head_dim: int) -> int:
@@ -104,15 +151,14 @@ def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_
     blk_q, blk_k, warp_q, warp_k = qk_config
     dev = q_int8.device
     lse = torch.empty((b, hq, nq) if return_lse else (0,), dtype=torch.float32, device=dev)
-    check = _check_status_enabled()
-    status = torch.zeros(4, dtype=torch.int32, device=dev) if check else None
+    status = _launch_status(dev)
     gran = C.GRAN_PER_THREAD if granularity == "per_thread" else C.GRAN_PER_BLOCK
     with torch.cuda.device(dev):
         if fp8:
             C.check(C.lib().sage_b200_attn_fwd_fp8(
                 q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), v_scale.data_ptr(), output.data_ptr(),
                 q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
-                status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
+                status.data_ptr(), C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
                 C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
                 C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
                 1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran, C.stream_ptr(dev)))
@@ -121,7 +167,7 @@ def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_
             C.check(C.lib().sage_b200_attn_fwd_fuse_v_mean(
                 q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), v_mean.data_ptr(), output.data_ptr(),
                 q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
-                status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
+                status.data_ptr(), C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
                 C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
                 C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
                 1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran, C.stream_ptr(dev)))
@@ -129,15 +175,12 @@ def attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_
             C.check(C.lib().sage_b200_attn_fwd(
                 q_int8.data_ptr(), k_int8.data_ptr(), v_fp16.data_ptr(), output.data_ptr(),
                 q_scale.data_ptr(), k_scale.data_ptr(), lse.data_ptr() if return_lse else 0,
-                status.data_ptr() if check else 0, C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
+                status.data_ptr(), C.dtype_code(output.dtype), b, hq, hkv, nq, nk, d,
                 C.bhn_strides(q_int8, tensor_layout), C.bhn_strides(k_int8, tensor_layout),
                 C.bhn_strides(v_fp16, tensor_layout), C.bhn_strides(output, tensor_layout),
                 1 if is_causal else 0, float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran,
                 _PV_CODE[pv_accum_dtype], C.stream_ptr(dev)))
-    if check:
-        st = status.tolist()
-        if st[0] != 0:
-            raise C.SageB200Error(f"attention kernel gave up waiting (code {st[0]}) in CTA {tuple(st[1:])}")
+    _after_launch(dev, status)
     return lse
 
 
@@ -163,20 +206,62 @@ def _sageattn_one_call(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth
     km = None
     if return_lse and smooth_k:
         km = torch.empty((b, hkv, 1, d) if tensor_layout == "HND" else (b, 1, hkv, d), dtype=k.dtype, device=dev)
-    check = _check_status_enabled()
-    status = torch.zeros(4, dtype=torch.int32, device=dev) if check else None
+    status = _launch_status(dev)
     with torch.cuda.device(dev):
         C.check(L.sage_b200_sageattn(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(), lse.data_ptr() if return_lse else 0,
-            km.data_ptr() if km is not None else 0, work.data_ptr(), nbytes, status.data_ptr() if check else 0,
+            km.data_ptr() if km is not None else 0, work.data_ptr(), nbytes, status.data_ptr(),
             dt, b, hq, hkv, nq, nk, d, C.bhn_strides(q, tensor_layout), C.bhn_strides(k, tensor_layout),
             C.bhn_strides(v, tensor_layout), C.bhn_strides(output, tensor_layout), 1 if is_causal else 0,
             float(sm_scale), blk_q, blk_k, warp_q, warp_k, gran, 1 if smooth_k else 0, _PV_CODE[pv_accum_dtype],
             Q._DIV[Q.default_div_mode()], C.stream_ptr(dev)))
-    if check:
-        st = status.tolist()
-        if st[0] != 0:
-            raise C.SageB200Error(f"attention kernel gave up waiting (code {st[0]}) in CTA {tuple(st[1:])}")
+    _after_launch(dev, status)
+    output = output[..., :head_dim]
+    if not return_lse:
+        return output
+    lse = lse / LOG2_E
+    if smooth_k:
+        lse = lse + _lse_correction(q, km, tensor_layout) * sm_scale
+    return output, lse
+
+
+def _sageattn_traceable(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v, return_lse, qk_config,
+                        sm_scale, qk_quant_gran, head_dim):
+    """The same path written with torch operators only (the natively registered ones of
+    sageattention/ops.py plus torch functions), which is what torch.compile traces.  Inputs are already
+    padded and aligned."""
+    from .ops import ops
+    blk_q, blk_k, warp_q, warp_k = qk_config
+    if qk_quant_gran == "per_warp":
+        blk_q, warp_k, qk_quant_gran = warp_q, blk_k, "per_block"
+    per_thread = qk_quant_gran == "per_thread"
+    layout = 1 if tensor_layout == "HND" else 0
+    div = Q._DIV[Q.default_div_mode()]
+    km = None
+    if not smooth_v and pv_accum_dtype in _PV_CODE:
+        output, lse, km = ops.sageattn(q, k, v, layout, is_causal, float(sm_scale), blk_q, blk_k, warp_q, warp_k,
+                                       C.GRAN_PER_THREAD if per_thread else C.GRAN_PER_BLOCK, smooth_k,
+                                       _PV_CODE[pv_accum_dtype], div, return_lse)
+    else:
+        q8, qs = ops.quant_int8(q, None, layout, blk_q, warp_q if per_thread else blk_q,
+                                C.GROUP_Q_THREAD if per_thread else C.GROUP_BLOCK, div)
+        km = ops.mean_k(k, layout) if smooth_k else None
+        k8, ks = ops.quant_int8(k, km, layout, blk_k, warp_k if per_thread else blk_k,
+                                C.GROUP_K_THREAD if per_thread else C.GROUP_BLOCK, div)
+        output = torch.empty(q.size(), dtype=q.dtype, device=q.device)
+        if not per_thread:
+            raise ValueError("under torch.compile the fp8 and smooth_v variants take qk_quant_gran='per_thread'.")
+        if pv_accum_dtype == _FP8_PV:
+            v8, vs = ops.quant_v_fp8(v, layout)
+            lse = ops.qk_int8_sv_f8_accum_f32_attn(q8, k8, v8, output, qs, ks, vs, layout, is_causal, float(sm_scale),
+                                                   blk_q, blk_k, warp_q, warp_k, return_lse)
+        else:                                                 # smooth_v with the fp16 accumulator
+            seq = 2 if tensor_layout == "HND" else 1
+            vm = ops.mean_k(v, layout)
+            v_s = (v - vm).to(torch.float16)
+            lse = ops.qk_int8_sv_f16_accum_f16_fuse_v_mean_attn(q8, k8, v_s, output, qs, ks, vm.squeeze(seq).contiguous(),
+                                                                layout, is_causal, float(sm_scale), blk_q, blk_k,
+                                                                warp_q, warp_k, return_lse)
     output = output[..., :head_dim]
     if not return_lse:
         return output
@@ -220,12 +305,15 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         elif pv_accum_dtype == _FP8_PV:
             raise ValueError("smooth_v goes with pv_accum_dtype='fp16' only.")
 
-    # TMA and the vector kernels need 16-byte aligned rows
+    # TMA and the vector kernels need 16-byte aligned rows (all three tensors are 16-bit: 8 elements)
     def _aligned(t):
-        return t if (t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
+        return t if (t.storage_offset() % 8 == 0 and all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
     q, k, v = _aligned(q), _aligned(k), _aligned(v)
 
     blk_q, blk_k, warp_q, warp_k = qk_config
+    if torch.compiler.is_compiling():
+        return _sageattn_traceable(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v, return_lse,
+                                   qk_config, sm_scale, qk_quant_gran, head_dim)
     if _profile is None and not smooth_v and pv_accum_dtype in _PV_CODE:
         return _sageattn_one_call(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, return_lse,
                                   qk_config, sm_scale, qk_quant_gran, head_dim)
@@ -275,10 +363,6 @@ def sageattn_qk_int8_pv_fp16_cuda(q, k, v, tensor_layout="HND", is_causal=False,
     """SageAttention forward: int8 Q.K^T, fp16 P.V.  Signature of the reference
     (cuda_attn.py:44-55) plus the keyword-only extras `sm_scale` and `qk_quant_gran`."""
     assert attn_mask is None
-    if torch.compiler.is_compiling() and not return_lse:
-        from .ops import sageattn_fixed
-        return sageattn_fixed(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v,
-                              -1.0 if sm_scale is None else float(sm_scale), qk_quant_gran)
     kv_len = k.size(2) if tensor_layout == "HND" else k.size(1)
     qk_config = select_qk_config(_padded_head_dim(q.size(-1)), is_causal, pv_accum_dtype, kv_len)
     return _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v,

@@ -57,7 +57,7 @@ def make_inputs(case: dict):
 
 
 CASES = [
-    # BASELINE config 1 (tiny correctness case)
+    # the tiny correctness case
     dict(name="c1_nhd_fp16_d64", seed=0, B=1, Hq=2, Hkv=2, N=256, D=64, dtype="float16",
          layout="NHD", smooth_k=True, attn=True),
     # ragged tail + biased K + GQA, bf16, HND
@@ -74,7 +74,8 @@ CASES = [
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("SAGE_REFERENCE_DIR"), required="SAGE_REFERENCE_DIR" not in os.environ,
+                    help="checkout of woct0rdho/sageattention-autotune (or set SAGE_REFERENCE_DIR)")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
 

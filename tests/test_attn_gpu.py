@@ -84,17 +84,17 @@ def test_core_ragged_lengths(N, Nkv, causal, mode, D):
 
 
 def test_core_per_block_config1():
-    """BASELINE config 1: B=1, H=2, N=256, D=64, fp16, NHD, non-causal, smooth_k, fp32, per-block 128/64."""
+    """The tiny correctness case: B=1, H=2, N=256, D=64, fp16, NHD, non-causal, smooth_k, fp32, per-block 128/64."""
     cuda_or_fail()
     q, k, v = make_qkv(1, 2, 2, 256, 64, torch.float16, "NHD", seed=0)
     out, _, qz = _run_core(q, k, v, "NHD", False, "fp32", gran="per_block")
     exp, _ = _oracle(qz, "NHD", False, "fp32", "per_block", torch.float16)
     _assert_close(out, exp, "config1")
+    # the quantiser is bit-exact given the same K mean: feed the oracle the mean the GPU computed
     from sageattention import quant
-    q8, qs, k8, ks = O.quant_per_block(q.cpu(), k.cpu(), O.mean_k(k.cpu(), "NHD"), 128, 64, "NHD")
-    if torch.equal(O.mean_k(k.cpu(), "NHD"), quant.mean_k(k, "NHD").cpu()):
-        assert torch.equal(qz[0].cpu(), q8) and torch.equal(qz[2].cpu(), k8)
-        assert torch.equal(qz[1].cpu(), qs) and torch.equal(qz[3].cpu(), ks)
+    q8, qs, k8, ks = O.quant_per_block(q.cpu(), k.cpu(), quant.mean_k(k, "NHD").cpu(), 128, 64, "NHD")
+    assert torch.equal(qz[0].cpu(), q8) and torch.equal(qz[2].cpu(), k8)
+    assert torch.equal(qz[1].cpu(), qs) and torch.equal(qz[3].cpu(), ks)
 
 
 def test_core_sm_scale_argument():
@@ -267,7 +267,7 @@ def test_sageattn_end_to_end_vs_sdpa(layout, dtype, causal):
 
 
 def test_sageattn_return_lse_gqa_causal():
-    """BASELINE config 3 in small: GQA, causal, bf16, NHD, outlier channels, return_lse.  The LSE
+    """The GQA prefill case in small: GQA, causal, bf16, NHD, outlier channels, return_lse.  The LSE
     (natural log, with the smooth-k correction added back) is checked against the CPU oracle run
     through the same pipeline, and loosely against exact attention (int8 error on outlier-heavy K
     dominates that distance)."""
@@ -285,7 +285,7 @@ def test_sageattn_return_lse_gqa_causal():
 
 
 def test_sageattn_linearity_in_v_at_full_size():
-    """Size-independent property on a BASELINE-sized head (N = 32768, D = 128, causal): the output is
+    """Size-independent property on a full-length head (N = 32768, D = 128, causal): the output is
     linear in V, and with V = const every row returns that constant."""
     import sageattention
     cuda_or_fail()
@@ -318,7 +318,7 @@ def test_errors_are_loud():
 
 
 # ---------------------------------------------------------------------------------------------------
-# fp8 (e4m3) P.V variant - BASELINE config 4's second variant.  The reference tree has no fp8 kernel
+# fp8 (e4m3) P.V variant (the video-DiT case's second variant).  The reference tree has no fp8 kernel
 # (parity unpinned): the checks are against the CPU emulation of the same scheme and against the
 # fp16-P.V result.
 # ---------------------------------------------------------------------------------------------------

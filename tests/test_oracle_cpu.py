@@ -103,6 +103,33 @@ def test_header_symbols_are_exported():
     assert lib.sage_b200_version() == 100
 
 
+def test_torch_operators_are_registered_natively_with_fakes():
+    """The operator library loads without a GPU, registers every operator of the namespace with the
+    reference's schema for the four attention operators (csrc/qattn/pybind_sm80.cpp:24-90), and the
+    fake implementations return the right shapes and dtypes on meta tensors."""
+    from sageattention import ops as sage_ops
+    ns = torch.ops.sageattention_b200
+    for name in sage_ops.ALL_OPS:
+        assert hasattr(ns, name), name
+    schema = str(ns.qk_int8_sv_f16_accum_f32_attn.default._schema)
+    assert schema == ("sageattention_b200::qk_int8_sv_f16_accum_f32_attn(Tensor query, Tensor key, Tensor value, "
+                      "Tensor(a!) output, Tensor query_scale, Tensor key_scale, int tensor_layout, bool is_causal, "
+                      "float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k, bool return_lse) -> Tensor")
+    q = torch.empty(2, 300, 8, 128, dtype=torch.bfloat16, device="meta")          # NHD
+    k = torch.empty(2, 300, 2, 128, dtype=torch.bfloat16, device="meta")
+    q8, qs = ns.quant_int8(q, None, 0, 128, 32, 0, 0)
+    k8, ks = ns.quant_int8(k, ns.mean_k(k, 0), 0, 64, 64, 1, 0)
+    assert q8.dtype == torch.int8 and q8.shape == q.shape and qs.shape == (2, 8, 3 * 4 * 8) and ks.shape == (2, 2, 5 * 4)
+    assert ns.mean_k(k, 0).shape == (2, 1, 2, 128) and ns.cast_v_f16(k, 0).dtype == torch.float16
+    lse = ns.qk_int8_sv_f16_accum_f16_attn_inst_buf(q8, k8, ns.cast_v_f16(k, 0), torch.empty_like(q), qs, ks, 0, True,
+                                                    0.1, 128, 64, 32, 64, True)
+    assert lse.shape == (2, 8, 300) and lse.dtype == torch.float32
+    out, lse, km = ns.sageattn(q, k, k, 0, True, 0.1, 128, 64, 32, 64, 0, True, 2, 0, False)
+    assert out.shape == q.shape and out.is_contiguous() and lse.shape == (0,) and km.shape == (0,)
+    v8, vs = ns.quant_v_fp8(k, 0)
+    assert v8.dtype == torch.float8_e4m3fn and vs.shape == (2, 2, 128)
+
+
 def test_argument_errors_do_not_need_a_gpu():
     from sageattention import _capi
     lib = _capi.lib()

@@ -143,7 +143,7 @@ def test_cast_v_is_exactly_torch_cast():
 
 
 def test_quant_idempotent_properties_at_full_size():
-    """Size-independent properties at a BASELINE-sized tensor: dequantised values stay within half
+    """Size-independent properties at a full-length tensor: dequantised values stay within half
     a step of the input and the scale equals max|x| / 127 (+1e-7) of its group."""
     from sageattention import quant
     cuda_or_fail()
