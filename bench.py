@@ -12,7 +12,15 @@ Prints ONE JSON line (rank 0).  `value` is effective attention TOPS, 4*B*H*N^2*D
 ranks, inputs resident in HBM; `e2e` is the same metric through the host-buffer API with the
 host<->device copies inside the timed region; `roofline` describes the attention kernel (timed
 with CUDA events inside the same steps); `cpu_baseline` is the CPU restatement of the algorithm
-timed on a bounded sample.  With --impl reference only that CPU restatement is timed.
+timed on a bounded sample; `ref_gpu` times the reference's own GPU kernels (its sm80 attention
+kernel compiled for sm_100 and its Triton quantisers as cubins, oracle/_ref) on the same inputs
+after the timed region; with more than one rank a second timed loop adds the NCCL all-gather of
+the output (`gather_ms_per_step`, `value_with_gather`).
+
+--impl reference times the reference itself, unmodified: when its kernels are present under
+oracle/_ref and a GPU is there, its Triton quantisers + sm80 attention kernel with the fixed
+(128, 64, 32, 64) configuration on the whole workload on one GPU; otherwise the CPU restatement
+(oracle/) on a bounded sample.
 """
 from __future__ import annotations
 
@@ -168,11 +176,114 @@ def cpu_baseline(w, seconds_hint=20.0):
     return {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port", "sample": sample}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel in the ncu capture named in
+# roofline.traffic_unit; re-measured whenever the kernel changes
+NCU_TRAFFIC_4K = 179.0e6
+
+REF_CFG = (128, 64, 32, 64)          # the reference's first candidate and fallback (sageattention/cuda_autotune.py:9-14)
+REF_OPS = {"fp32": "qk_int8_sv_f16_accum_f32_attn", "fp16": "qk_int8_sv_f16_accum_f16_attn",
+           "fp16+fp32": "qk_int8_sv_f16_accum_f16_attn_inst_buf"}
+
+
+def reference_gpu_available(w) -> bool:
+    from oracle import triton_ref
+    so = os.path.join(ROOT, "oracle", "_ref", "libsage_ref_sm80.so")
+    return torch.cuda.is_available() and os.path.exists(so) and triton_ref.available() and w["pv"] in REF_OPS
+
+
+def reference_gpu_step(w):
+    """One forward pass the way the reference's CUDA backend runs it (sageattention/cuda_attn.py:126-274):
+    torch mean, its Triton per-thread quantisers, torch cast of V, its sm80 attention kernel.  Returns
+    a callable step(q, k, v) and a dict the callable fills with per-section CUDA events."""
+    from oracle import triton_ref
+    torch.ops.load_library(os.path.join(ROOT, "oracle", "_ref", "libsage_ref_sm80.so"))
+    op = getattr(torch.ops.sageattention_qattn_sm80, REF_OPS[w["pv"]])
+    layout = w["layout"]
+    seq = 2 if layout == "HND" else 1
+    code = 1 if layout == "HND" else 0
+    ev = {}
+
+    def mark(name):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        ev.setdefault(name, []).append(e)
+
+    def step(q, k, v):
+        out = torch.empty_like(q)
+        mark("t0")
+        km = k.mean(dim=seq, keepdim=True)
+        q8, qs, k8, ks = triton_ref.per_thread_int8(q, k, km, REF_CFG[0], REF_CFG[2], REF_CFG[1], REF_CFG[3], layout)
+        v16 = v.to(torch.float16)
+        mark("t1")
+        op(q8, k8, v16, out, qs, ks, code, w["causal"], w["D"] ** -0.5, *REF_CFG, False)
+        mark("t2")
+        return out
+    return step, ev
+
+
 def run_reference(args, w):
-    """--impl reference: the reference has no CPU implementation of this path (its kernels are CUDA
-    and Triton only), so the arm times the CPU restatement in oracle/ on the host cores."""
+    """--impl reference.  The reference has no CPU implementation of this path; its GPU kernels built
+    from its own sources (oracle/_ref) are timed when they and a GPU are present, else the CPU
+    restatement in oracle/ on a bounded sample."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    common = {"impl": "reference", "metric": "effective attention TOPS (4*B*H*N^2*D/t)", "unit": "TOPS",
+              "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+              "scaling": "strong", "vs_baseline": None, "data": "synthetic"}
+    cfg = {"workload": args.workload, **{k: w[k] for k in ("B", "Hq", "Hkv", "N", "D", "causal", "pv", "layout")}}
+    if reference_gpu_available(w):
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        q, k, v = make_inputs(w, 0, w["Hkv"], dev)
+        step, ev = reference_gpu_step(w)
+        sampler = ClockSampler(dev.index)
+        sampler.start()
+        for _ in range(max(3, args.warmup)):
+            step(q, k, v)
+        torch.cuda.synchronize()
+        ev.clear()
+        t_begin = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step(q, k, v)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop(t_begin, time.perf_counter())
+        ms = e0.elapsed_time(e1) / args.steps
+        front = sum(a.elapsed_time(b) for a, b in zip(ev["t0"], ev["t1"])) / args.steps
+        attn = sum(a.elapsed_time(b) for a, b in zip(ev["t1"], ev["t2"])) / args.steps
+        value = literal_flops(w, w["Hq"]) / (ms * 1e-3) / 1e12
+        # end to end the way a user of the reference would run it from host memory: copy in, call, copy out
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+        hout = torch.empty(hq.shape, dtype=hq.dtype, pin_memory=True)
+        del q, k, v
+
+        def step_host():
+            dq, dk, dv = (t.to(dev, non_blocking=True) for t in (hq, hk, hv))
+            hout.copy_(step(dq, dk, dv), non_blocking=True)
+        step_host()
+        torch.cuda.synchronize()
+        n_e2e = max(2, min(args.steps, 5))
+        e0.record()
+        for _ in range(n_e2e):
+            step_host()
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1) / n_e2e
+        line = dict(common, value=value, ms_per_step=ms, dtype="int8 QK^T + fp16 PV (reference sm80 mma.sync kernel)",
+                    config=dict(cfg, note="the reference's own kernels, unmodified, compiled for sm_100 (oracle/_ref): Triton "
+                                          "per-thread quantisers + sm80 attention kernel, fixed config (128, 64, 32, 64), whole "
+                                          "workload on ONE GPU whatever --gpus says (the reference is single-GPU)"),
+                    clocks=clocks, kernel_ms={"mean+quant+cast": front, "attn": attn},
+                    cpu_baseline={"value": value, "unit": "TOPS", "cores": 0, "kind": "reference",
+                                  "sample": "whole workload, on the GPU (the reference has no CPU path)"},
+                    e2e={"value": literal_flops(w, w["Hq"]) / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
+                         "h2d_bytes_per_step": int(sum(t.numel() * t.element_size() for t in (hq, hk, hv))),
+                         "d2h_bytes_per_step": int(hout.numel() * hout.element_size()),
+                         "api": "pinned host tensors copied in, the reference's call, result copied out to pinned memory"})
+        print(json.dumps(line))
         return
     vals = []
     total = args.warmup + args.steps
@@ -187,14 +298,9 @@ def run_reference(args, w):
     wall = time.perf_counter() - t_all
     value = statistics.mean(vals)
     base["value"] = value
-    line = {"impl": "reference", "metric": "effective attention TOPS (4*B*H*N^2*D/t)", "value": value, "unit": "TOPS",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": 1e3 * wall / total, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "int8 QK^T + fp16 PV (fp32 CPU emulation)", "data": "synthetic",
-            "config": {"workload": args.workload, **{k: w[k] for k in ("B", "Hq", "Hkv", "N", "D", "causal", "pv", "layout")},
-                       "note": "CPU restatement (oracle/) on host cores; each step is the bounded sample in cpu_baseline.sample"},
-            "cpu_baseline": base,
-            "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    line = dict(common, value=value, ms_per_step=1e3 * wall / total, dtype="int8 QK^T + fp16 PV (fp32 CPU emulation)",
+                config=dict(cfg, note="CPU restatement (oracle/) on host cores; each step is the bounded sample in cpu_baseline.sample"),
+                cpu_baseline=base, e2e={"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
     print(json.dumps(line))
 
 
@@ -207,7 +313,8 @@ def main():
     ap.add_argument("--workload", default="c5_32k", choices=sorted(WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--gather", action="store_true", help="also time the NCCL all-gather of the output")
+    ap.add_argument("--no-gather", action="store_true", help="skip the second timed loop with the NCCL all-gather")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels after the run")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -218,7 +325,8 @@ def main():
     import sageattention
     from sageattention import core as sa_core
     from sageattention.host import sageattn_host
-    from sageattention.parallel import local_heads
+    from sageattention.parallel import local_heads, sageattn_sharded
+    from sageattention import _capi as sa_capi
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -270,7 +378,9 @@ def main():
         step()
     barrier()
     t_begin = time.perf_counter()
+    launches_before = sa_capi.lib().sage_b200_launch_count()
     total_ms = timed(step, args.steps, 0)
+    launches = sa_capi.lib().sage_b200_launch_count() - launches_before      # this rank's, counted by the library
     clocks = sampler.stop(t_begin, time.perf_counter())
     # ---- the same steps once more, through the step-by-step path with CUDA events around every section
     # (quantisers, K mean, V cast, attention kernel): the per-kernel times the roofline is computed from
@@ -294,10 +404,10 @@ def main():
     peak_mixed = pk["bf16_sustained"] * 4.0 / 3.0
     roofline = {"bound": "tensor", "kernel": "sage_attn_fwd_kernel", "achieved": achieved, "peak": peak_mixed,
                 "unit": "TFLOP/s", "frac": (achieved / peak_mixed) if achieved else None,
-                # dram__bytes_read+write of an ncu capture at N=4096, H=64 (profiles/attn_fwd_fp16fp32_c5_4k.md),
-                # scaled by the number of Q/K/V/O elements of this rank (all terms are linear in them)
-                "traffic": 179.0e6 * (w["B"] * heads_local * w["N"] * w["D"]) / (64 * 4096 * 128) if w["D"] == 128 else None,
-                "traffic_unit": "bytes per launch (scaled from a 4k capture)",
+                # dram__bytes_read + dram__bytes_write of one ncu capture of this kernel (B=1, H=64, N=4096, D=128,
+                # causal), scaled by this rank's Q/K/V/O element count: every term is linear in it
+                "traffic": NCU_TRAFFIC_4K * (w["B"] * heads_local * w["N"] * w["D"]) / (64 * 4096 * 128) if w["D"] == 128 else None,
+                "traffic_unit": "bytes per launch, scaled from the ncu capture of the B=1 H=64 N=4096 D=128 causal case",
                 "peak_source": f"{pk['source']}: 4/3 x sustained dense bf16 ({pk['bf16_sustained']} TF/s); int8 counted at 2x bf16",
                 "frac_of_int8_peak_literal": (literal_flops(w, heads_local) / (attn_ms * 1e-3) / 1e12) / (2 * pk["bf16_sustained"]) if attn_ms else None,
                 "kernel_ms": kern_ms, "kernel_ms_pass": "second pass of the same steps, per-section CUDA events",
@@ -311,14 +421,13 @@ def main():
                          "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": (qbytes / (front_ms * 1e-3) / 1e9) / pk["hbm_gbs"] if front_ms else None}
 
-    # ---- optional all-gather of the output
+    # ---- the same step with the output all-gathered over NCCL (every rank ends with all heads), overlapped
+    # with the compute per head group by sageattn_sharded
     gather_ms = None
-    if args.gather and world > 1:
-        full = torch.empty((world,) + tuple(out_holder["o"].shape), dtype=out_holder["o"].dtype, device=dev)
-
+    if world > 1 and not args.no_gather:
         def step_gather():
-            step()
-            dist.all_gather_into_tensor(full, out_holder["o"].contiguous())
+            out_holder["g"] = sageattn_sharded(q, k, v, num_q_heads=w["Hq"], num_kv_heads=w["Hkv"], gather=True,
+                                               attn_fn=attn_call, **kw)
         gather_ms = timed(step_gather, args.steps, 2) / args.steps
 
     # ---- end to end from pinned host memory
@@ -339,7 +448,6 @@ def main():
     if world > 1:
         dist.barrier()
     if rank == 0:
-        launches_per_step = 2 + 2 + 1 + (1 if w["dtype"] == "bfloat16" else 0)   # mean (2), quant q/k, attention, V cast
         line = {"metric": "effective attention TOPS (4*B*H*N^2*D/t)", "value": value, "unit": "TOPS",
                 "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -349,8 +457,26 @@ def main():
                            "l2": "inputs (1.6 GB per step at N=32k) exceed the 126 MB L2; no flush needed"},
                 "executed_tops": value * (0.5 if w["causal"] else 1.0),
                 "clocks": clocks, "roofline": roofline, "e2e": e2e,
-                "gpu_launches": launches_per_step * args.steps,
-                "gather_ms_per_step": gather_ms}
+                "gpu_launches": int(launches) * world,
+                "gpu_launches_note": "kernels of libsage_b200.so launched inside the timed region, counted by the library "
+                                     "(sage_b200_launch_count) on rank 0, times the number of ranks",
+                "gather_ms_per_step": gather_ms,
+                "value_with_gather": (F_lit / (gather_ms * 1e-3) / 1e12) if gather_ms else None}
+        if not args.no_ref_gpu and world == 1 and reference_gpu_available(w):
+            # the reference's own GPU kernels on the same inputs, after (never inside) the timed region
+            rstep, ev = reference_gpu_step(w)
+            for _ in range(2):
+                rstep(q, k, v)
+            torch.cuda.synchronize()
+            ev.clear()
+            n_ref = max(2, min(args.steps, 5))
+            for _ in range(n_ref):
+                rstep(q, k, v)
+            torch.cuda.synchronize()
+            line["ref_gpu"] = {"quant_ms": sum(a.elapsed_time(b) for a, b in zip(ev["t0"], ev["t1"])) / n_ref,
+                               "attn_ms": sum(a.elapsed_time(b) for a, b in zip(ev["t1"], ev["t2"])) / n_ref,
+                               "kind": "the reference's sm80 kernel compiled for sm_100 + its Triton quantisers as cubins "
+                                       "(oracle/_ref), fixed config (128, 64, 32, 64), same inputs, after the timed region"}
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line))

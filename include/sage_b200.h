@@ -58,8 +58,34 @@ extern "C" {
 #define SAGE_B200_PV_F16_F32 2   /* "fp16+fp32" */
 #define SAGE_B200_PV_F8      3   /* fp8 e4m3 P and V, fp32 accumulate (sage_b200_attn_fwd_fp8 only) */
 
+/* kernels of the attention core (sage_b200_tile_entry.kernel) */
+#define SAGE_B200_KERNEL_TWO_TILE         0  /* 256 query rows per CTA share every K/V block; O accumulates in tensor memory */
+#define SAGE_B200_KERNEL_ONE_TILE_FOLD    1  /* 128 query rows per CTA, fp16 partial products folded into fp32 by a fold warpgroup */
+#define SAGE_B200_KERNEL_TWO_TILE_COUPLED 2  /* the two-level mode inside the two-tile kernel's softmax warps */
+
+/*
+ * One entry of the fixed tile table.  Replaces the reference's run-time selection among
+ * _AUTOTUNE_CONFIGS (sageattention/cuda_autotune.py:9-41): the scale grouping a problem is quantised
+ * and attended with, and the kernel configuration that runs it, chosen from measurements on B200.
+ */
+typedef struct sage_b200_tile_entry {
+  int blk_q, blk_k, warp_q, warp_k;  /* which query rows and keys share an int8 scale */
+  int kernel;                        /* SAGE_B200_KERNEL_* */
+  int q_tiles_per_cta;               /* 128-row query tiles per CTA */
+  int seq_bucket;                    /* index of the key-length bucket the entry was looked up in */
+} sage_b200_tile_entry;
+
+/* head_dim 64 / 128 / 256 (after padding), pv_accum one of SAGE_B200_PV_*.  Returns SAGE_B200_OK or
+ * SAGE_B200_ERR_INVALID.  sage_b200_attn_fwd consults the same table for the kernel and the tiles per
+ * CTA; the grouping is the caller's to pass to the quantisers and to sage_b200_attn_fwd alike. */
+int sage_b200_tile_lookup(int head_dim, int is_causal, int pv_accum, int len_kv, sage_b200_tile_entry* entry);
+
 int sage_b200_version(void);
 const char* sage_b200_last_error(void);
+/* Number of kernels this library has launched in this process so far (all threads, all devices).  The
+ * reference has no counterpart; benchmarks use it to state how many of the library's own kernels ran
+ * inside a timed region. */
+unsigned long long sage_b200_launch_count(void);
 
 /*
  * Channel mean of K over the sequence, rounded to K's dtype.

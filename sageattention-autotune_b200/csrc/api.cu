@@ -1,4 +1,6 @@
 // Error reporting and version entry points of the C ABI.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace sage {
@@ -16,7 +18,17 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+bool& pdl_chain_flag() {
+  static thread_local bool flag = false;
+  return flag;
+}
+
 }  // namespace sage
+
+extern "C" unsigned long long sage_b200_launch_count(void) { return sage::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int sage_b200_version(void) { return SAGE_B200_VERSION; }
 
@@ -103,9 +115,13 @@ extern "C" int sage_b200_sageattn(const void* q, const void* k, const void* v, v
   const int64_t q8_st[3] = {int64_t(heads_q) * len_q * head_dim, int64_t(len_q) * head_dim, head_dim};
   const int64_t k8_st[3] = {int64_t(heads_kv) * len_kv * head_dim, int64_t(len_kv) * head_dim, head_dim};
 
+  // the first kernel is an ordinary launch (it must not overtake whatever used this memory before);
+  // every later one may be placed while its predecessor drains
+  PdlChain chain;
   int rc = sage_b200_quant_int8(q, nullptr, q8, qs, dtype, batch, heads_q, len_q, head_dim, q_strides, q8_st, blk_q,
                                 p.q_warp, p.q_kind, div_mode, stream);
   if (rc != SAGE_B200_OK) return rc;
+  chain.arm();
   if (smooth_k) {
     rc = sage_b200_mean_k(k, km, w + p.scratch, p.v16 - p.scratch, dtype, batch, heads_kv, len_kv, head_dim, k_strides, stream);
     if (rc != SAGE_B200_OK) return rc;

@@ -8,6 +8,7 @@
 #include "attn_common.cuh"
 #include "attn_v1.cuh"
 #include "attn_v4.cuh"
+#include "tile_table.h"
 
 namespace sage {
 
@@ -53,49 +54,64 @@ static int make_map(CUtensorMap* map, const void* base, int elem_bytes, int batc
   return SAGE_B200_OK;
 }
 
+// Environment overrides of the tile table, for sweeps: SAGE_B200_KERNEL=coupled runs the two-level mode on
+// the two-tile kernel, SAGE_B200_QTILES=1|2 fixes the query tiles per CTA of the two-tile kernel.
+static int env_int(const char* name) {
+  const char* e = getenv(name);
+  return (e != nullptr && e[0] >= '0' && e[0] <= '9') ? atoi(e) : -1;
+}
+
 template <int D, int PV_MODE, int OUT_DTYPE, int KSUB>
 static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
-                       dim3 grid, cudaStream_t stream) {
-  // Two kernels exist.  fp32, fp16 and fp8 accumulation run the two-tile kernel (attn_v1.cuh: 256 query
+                       cudaStream_t stream) {
+  // Two kernels exist.  fp32, fp16 and fp8 accumulation run the two-tile kernel (attn_v1.cuh: up to 256 query
   // rows per CTA share every K/V block, the output accumulates in tensor memory).  The two-level
   // "fp16+fp32" mode needs an fp16 partial product next to the scores and runs the one-tile kernel with
-  // a fold warpgroup (attn_v4.cuh); SAGE_B200_KERNEL=coupled runs it on the two-tile kernel instead,
-  // which folds inside the softmax warps (slower, kept as a cross-check).  KSUB = 2 (scale blocks of
-  // 32 keys, the reference's (128, 32, 32, 32) candidate) is built into the two-tile kernel only.
+  // a fold warpgroup (attn_v4.cuh) wherever the tile table says so; on the two-tile kernel it folds
+  // inside the softmax warps.  KSUB = 2 (scale blocks of 32 keys, the reference's (128, 32, 32, 32)
+  // candidate) is built into the two-tile kernel only.
   void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const AttnParams) = nullptr;
   int smem = 0;
   int threads = kAttnThreads;
   int which = 0;               // index of the kernel in the per-device attribute cache below
-  if constexpr (PV_MODE == SAGE_B200_PV_F16_F32) {
-    static const bool two_tile = [] {
-      const char* e = getenv("SAGE_B200_KERNEL");
-      return e != nullptr && e[0] == 'c';
-    }();
-    if constexpr (D == 256 || KSUB != 1) {
-      // 256 channels of fp16 partial product and of fp32 output do not fit the one-tile kernel's
-      // tensor memory and registers: the mode folds 64 channels at a time inside the softmax warps
-      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
-      smem = v1::SmemPlan<D>::kDynamic;
-    } else if (two_tile) {
-      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE>;
-      smem = v1::SmemPlan<D>::kDynamic;
-    } else {
+  sage_b200_tile_entry te = tile_lookup(D, p.causal, PV_MODE, p.len_kv);
+  static const bool force_coupled = [] {
+    const char* e = getenv("SAGE_B200_KERNEL");
+    return e != nullptr && e[0] == 'c';
+  }();
+  static const int force_tiles = env_int("SAGE_B200_QTILES");
+  if (force_coupled && te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD) te.kernel = SAGE_B200_KERNEL_TWO_TILE_COUPLED, te.q_tiles_per_cta = 2;
+  if ((force_tiles == 1 || force_tiles == 2) && te.kernel != SAGE_B200_KERNEL_ONE_TILE_FOLD && D != 256)
+    te.q_tiles_per_cta = force_tiles;
+  bool one_tile_fold = false;
+  if constexpr (PV_MODE == SAGE_B200_PV_F16_F32 && D != 256 && KSUB == 1) {
+    one_tile_fold = (te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD);
+    if (one_tile_fold) {
       kern = v4::sage_attn_fwd_kernel<D, OUT_DTYPE>;
       smem = v4::SmemPlan<D>::kDynamic;
-      grid.x = (p.len_q + kTileQ - 1) / kTileQ;
       threads = v4::kThreads;
       which = 1;
     }
-  } else if constexpr (PV_MODE == SAGE_B200_PV_F8) {
-    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
-    smem = v1::SmemPlan<D, true>::kDynamic;
-  } else {
-    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
-    smem = v1::SmemPlan<D>::kDynamic;
   }
+  constexpr bool kFp8 = (PV_MODE == SAGE_B200_PV_F8);
+  // (an entry that names the one-tile kernel for a configuration only the two-tile kernel is built for
+  // falls back to two tiles per CTA)
+  const int tiles = (one_tile_fold || D == 256) ? 1 : (te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD ? 2 : te.q_tiles_per_cta);
+  if (!one_tile_fold) {
+    if (tiles == 1 && D != 256) {
+      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB, 1>;
+      smem = v1::SmemPlan<D, kFp8, 1>::kDynamic;
+      which = 2;
+    } else {
+      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB, 2>;
+      smem = v1::SmemPlan<D, kFp8, 2>::kDynamic;
+    }
+  }
+  const int rows_per_cta = tiles * kTileQ;
+  const dim3 grid((p.len_q + rows_per_cta - 1) / rows_per_cta, p.heads_q, p.batch);
   cudaError_t attr_err = cudaSuccess;
   // the attribute is per device: set it for every device that launches
-  static bool done[2][64] = {};
+  static bool done[3][64] = {};
   static std::mutex mu;
   int dev = 0;
   SAGE_CUDA_TRY(cudaGetDevice(&dev));
@@ -108,26 +124,25 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
       if (dev >= 0 && dev < 64) done[which][dev] = true;
     }
   }
-  kern<<<grid, threads, smem, stream>>>(mq, mk, mv, p);
-  SAGE_CUDA_TRY(cudaGetLastError());
+  SAGE_CUDA_TRY(launch_kernel(kern, grid, dim3(threads), smem, stream, mq, mk, mv, p));
   return SAGE_B200_OK;
 }
 
 template <int D, int PV_MODE, int KSUB>
 static int launch_attn_out(int out_dtype, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                           const AttnParams& p, dim3 grid, cudaStream_t stream) {
-  if (out_dtype == SAGE_B200_BF16) return launch_attn<D, PV_MODE, SAGE_B200_BF16, KSUB>(mq, mk, mv, p, grid, stream);
-  return launch_attn<D, PV_MODE, SAGE_B200_F16, KSUB>(mq, mk, mv, p, grid, stream);
+                           const AttnParams& p, cudaStream_t stream) {
+  if (out_dtype == SAGE_B200_BF16) return launch_attn<D, PV_MODE, SAGE_B200_BF16, KSUB>(mq, mk, mv, p, stream);
+  return launch_attn<D, PV_MODE, SAGE_B200_F16, KSUB>(mq, mk, mv, p, stream);
 }
 
 template <int D, int KSUB>
 static int launch_attn_mode(int pv_accum, int out_dtype, const CUtensorMap& mq, const CUtensorMap& mk,
-                            const CUtensorMap& mv, const AttnParams& p, dim3 grid, cudaStream_t stream) {
+                            const CUtensorMap& mv, const AttnParams& p, cudaStream_t stream) {
   switch (pv_accum) {
-    case SAGE_B200_PV_F32: return launch_attn_out<D, SAGE_B200_PV_F32, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
-    case SAGE_B200_PV_F16: return launch_attn_out<D, SAGE_B200_PV_F16, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
-    case SAGE_B200_PV_F8: return launch_attn_out<D, SAGE_B200_PV_F8, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
-    default: return launch_attn_out<D, SAGE_B200_PV_F16_F32, KSUB>(out_dtype, mq, mk, mv, p, grid, stream);
+    case SAGE_B200_PV_F32: return launch_attn_out<D, SAGE_B200_PV_F32, KSUB>(out_dtype, mq, mk, mv, p, stream);
+    case SAGE_B200_PV_F16: return launch_attn_out<D, SAGE_B200_PV_F16, KSUB>(out_dtype, mq, mk, mv, p, stream);
+    case SAGE_B200_PV_F8: return launch_attn_out<D, SAGE_B200_PV_F8, KSUB>(out_dtype, mq, mk, mv, p, stream);
+    default: return launch_attn_out<D, SAGE_B200_PV_F16_F32, KSUB>(out_dtype, mq, mk, mv, p, stream);
   }
 }
 
@@ -192,6 +207,7 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   p.len_kv = len_kv;
   p.heads_q = heads_q;
   p.heads_kv = heads_kv;
+  p.batch = batch;
   const int q_blocks = (len_q + blk_q - 1) / blk_q, k_blocks = (len_kv + blk_k - 1) / blk_k;
   if (granularity == SAGE_B200_GRAN_PER_THREAD) {
     p.q_groups = q_blocks * (blk_q / warp_q) * 8;
@@ -224,18 +240,24 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
     rc = make_map(&mv, v, 2, batch, heads_kv, len_kv, head_dim, v_strides, 64, kStageRows, CU_TENSOR_MAP_SWIZZLE_128B, "v");
   if (rc) return rc;
 
-  const int rows_per_cta = (head_dim == 256 ? 1 : 2) * kTileQ;     // the one-tile kernel resets grid.x itself
-  const dim3 grid((len_q + rows_per_cta - 1) / rows_per_cta, heads_q, batch);
   if (blk_k == 32) {
-    if (head_dim == 64) return launch_attn_mode<64, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
-    if (head_dim == 256) return launch_attn_mode<256, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
-    return launch_attn_mode<128, 2>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+    if (head_dim == 64) return launch_attn_mode<64, 2>(pv_accum, out_dtype, mq, mk, mv, p, stream);
+    if (head_dim == 256) return launch_attn_mode<256, 2>(pv_accum, out_dtype, mq, mk, mv, p, stream);
+    return launch_attn_mode<128, 2>(pv_accum, out_dtype, mq, mk, mv, p, stream);
   }
-  if (head_dim == 64) return launch_attn_mode<64, 1>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
-  if (head_dim == 256) return launch_attn_mode<256, 1>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
-  return launch_attn_mode<128, 1>(pv_accum, out_dtype, mq, mk, mv, p, grid, stream);
+  if (head_dim == 64) return launch_attn_mode<64, 1>(pv_accum, out_dtype, mq, mk, mv, p, stream);
+  if (head_dim == 256) return launch_attn_mode<256, 1>(pv_accum, out_dtype, mq, mk, mv, p, stream);
+  return launch_attn_mode<128, 1>(pv_accum, out_dtype, mq, mk, mv, p, stream);
 }
 
+
+extern "C" int sage_b200_tile_lookup(int head_dim, int is_causal, int pv_accum, int len_kv, sage_b200_tile_entry* entry) {
+  SAGE_REQUIRE(entry != nullptr, "tile_lookup: null entry");
+  SAGE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "tile_lookup: head_dim must be 64, 128 or 256");
+  SAGE_REQUIRE(pv_accum >= 0 && pv_accum <= 3 && len_kv > 0, "tile_lookup: bad pv_accum or length");
+  *entry = tile_lookup(head_dim, is_causal, pv_accum, len_kv);
+  return SAGE_B200_OK;
+}
 
 extern "C" int sage_b200_attn_fwd(const int8_t* q, const int8_t* k, const void* v, void* out,
                                   const float* q_scale, const float* k_scale, float* lse, int32_t* status,

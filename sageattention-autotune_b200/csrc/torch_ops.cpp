@@ -69,6 +69,14 @@ void check_rc(int rc) { STD_TORCH_CHECK(rc == SAGE_B200_OK, "sage_b200 error ", 
 
 std::vector<int64_t> shape_like(const Tensor& t) { return {t.size(0), t.size(1), t.size(2), t.size(3)}; }
 
+// TMA and the 16-byte vector kernels need a 16-byte aligned base and strides that are multiples of
+// 8 elements; anything else (a view that starts at an odd offset, odd strides) is copied once
+Tensor aligned16(const Tensor& t) {
+  const bool ok = (reinterpret_cast<uintptr_t>(t.const_data_ptr()) & 15u) == 0 && t.stride(0) % 8 == 0 &&
+                  t.stride(1) % 8 == 0 && t.stride(2) % 8 == 0;
+  return ok ? t : torch::stable::contiguous(t);
+}
+
 // ------------------------------------------------------------------------------------ attention core
 Tensor attn_common(const Tensor& query, const Tensor& key, const Tensor& value, const Tensor& output,
                    const Tensor& query_scale, const Tensor& key_scale, const Tensor* value_mean,
@@ -177,8 +185,9 @@ Tensor qk_int8_sv_f16_attn_per_block(const Tensor& query, const Tensor& key, con
 
 // ------------------------------------------------------------------------------------ front end
 // k.mean(dim=seq, keepdim=True) in k's dtype (sageattention/cuda_attn.py:167-170)
-Tensor mean_k(const Tensor& k, int64_t tensor_layout) {
-  check_cuda_lastdim(k, "k");
+Tensor mean_k(const Tensor& k_in, int64_t tensor_layout) {
+  check_cuda_lastdim(k_in, "k");
+  const Tensor k = aligned16(k_in);
   const Dims d = dims_of(k, tensor_layout);
   const int dt = dtype_code(k);
   const torch::stable::accelerator::DeviceGuard guard(k.get_device_index());
@@ -195,9 +204,10 @@ Tensor mean_k(const Tensor& k, int64_t tensor_layout) {
 
 // (int8 tensor, fp32 scales): group_kind 0 = Q per-thread, 1 = K per-thread, 2 = per block
 // (sageattention/triton/quant_per_thread.py:118-205, quant_per_block.py:81-173)
-std::tuple<Tensor, Tensor> quant_int8(const Tensor& x, const std::optional<Tensor>& mean, int64_t tensor_layout,
+std::tuple<Tensor, Tensor> quant_int8(const Tensor& x_in, const std::optional<Tensor>& mean, int64_t tensor_layout,
                                       int64_t blk, int64_t warp, int64_t group_kind, int64_t div_mode) {
-  check_cuda_lastdim(x, "x");
+  check_cuda_lastdim(x_in, "x");
+  const Tensor x = aligned16(x_in);
   const Dims d = dims_of(x, tensor_layout);
   const int dt = dtype_code(x);
   STD_TORCH_CHECK(blk > 0 && warp > 0 && warp <= blk, "bad blk / warp");
@@ -224,8 +234,9 @@ std::tuple<Tensor, Tensor> quant_int8(const Tensor& x, const std::optional<Tenso
 }
 
 // v.to(torch.float16) (sageattention/cuda_attn.py:195)
-Tensor cast_v_f16(const Tensor& v, int64_t tensor_layout) {
-  check_cuda_lastdim(v, "v");
+Tensor cast_v_f16(const Tensor& v_in, int64_t tensor_layout) {
+  check_cuda_lastdim(v_in, "v");
+  const Tensor v = aligned16(v_in);
   const Dims d = dims_of(v, tensor_layout);
   const int dt = dtype_code(v);
   const torch::stable::accelerator::DeviceGuard guard(v.get_device_index());
@@ -237,8 +248,9 @@ Tensor cast_v_f16(const Tensor& v, int64_t tensor_layout) {
 }
 
 // (v as e4m3 bytes, fp32 scale per (batch, head, channel))
-std::tuple<Tensor, Tensor> quant_v_fp8(const Tensor& v, int64_t tensor_layout) {
-  check_cuda_lastdim(v, "v");
+std::tuple<Tensor, Tensor> quant_v_fp8(const Tensor& v_in, int64_t tensor_layout) {
+  check_cuda_lastdim(v_in, "v");
+  const Tensor v = aligned16(v_in);
   const Dims d = dims_of(v, tensor_layout);
   const int dt = dtype_code(v);
   const torch::stable::accelerator::DeviceGuard guard(v.get_device_index());
@@ -256,13 +268,14 @@ std::tuple<Tensor, Tensor> quant_v_fp8(const Tensor& v, int64_t tensor_layout) {
 // The whole forward path in one operator (sageattention/cuda_attn.py:126-274 from the K mean to the
 // attention kernel).  Returns (output, lse, km): lse is base 2 without the smooth-k correction and
 // empty unless return_lse; km is the K mean, empty unless smooth_k and return_lse.
-std::tuple<Tensor, Tensor, Tensor> sageattn(const Tensor& q, const Tensor& k, const Tensor& v, int64_t tensor_layout,
-                                            bool is_causal, double sm_scale, int64_t blk_q, int64_t blk_k,
-                                            int64_t warp_q, int64_t warp_k, int64_t granularity, bool smooth_k,
-                                            int64_t pv_accum, int64_t div_mode, bool return_lse) {
-  check_cuda_lastdim(q, "q");
-  check_cuda_lastdim(k, "k");
-  check_cuda_lastdim(v, "v");
+std::tuple<Tensor, Tensor, Tensor> sageattn(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in,
+                                            int64_t tensor_layout, bool is_causal, double sm_scale, int64_t blk_q,
+                                            int64_t blk_k, int64_t warp_q, int64_t warp_k, int64_t granularity,
+                                            bool smooth_k, int64_t pv_accum, int64_t div_mode, bool return_lse) {
+  check_cuda_lastdim(q_in, "q");
+  check_cuda_lastdim(k_in, "k");
+  check_cuda_lastdim(v_in, "v");
+  const Tensor q = aligned16(q_in), k = aligned16(k_in), v = aligned16(v_in);
   const Dims dq = dims_of(q, tensor_layout), dk = dims_of(k, tensor_layout), dv = dims_of(v, tensor_layout);
   const int dt = dtype_code(q);
   STD_TORCH_CHECK(dtype_code(k) == dt && dtype_code(v) == dt, "q, k and v must have the same dtype");

@@ -26,7 +26,7 @@ EXPORTS = (
     "sage_b200_quant_int8", "sage_b200_smooth_quant_k_scratch_bytes", "sage_b200_smooth_quant_k",
     "sage_b200_cast_v_f16", "sage_b200_attn_fwd", "sage_b200_quant_v_fp8_scratch_bytes", "sage_b200_quant_v_fp8",
     "sage_b200_attn_fwd_fp8", "sage_b200_smooth_v_f16", "sage_b200_attn_fwd_fuse_v_mean",
-    "sage_b200_sageattn_workspace_bytes", "sage_b200_sageattn", "sage_b200_set_wait_budget",
+    "sage_b200_sageattn_workspace_bytes", "sage_b200_sageattn", "sage_b200_set_wait_budget", "sage_b200_launch_count", "sage_b200_tile_lookup",
 )
 
 _lib = None
@@ -35,6 +35,12 @@ _I64x3 = ctypes.c_int64 * 3
 
 class SageB200Error(RuntimeError):
     pass
+
+
+class TileEntry(ctypes.Structure):
+    """sage_b200_tile_entry of include/sage_b200.h"""
+    _fields_ = [("blk_q", ctypes.c_int), ("blk_k", ctypes.c_int), ("warp_q", ctypes.c_int), ("warp_k", ctypes.c_int),
+                ("kernel", ctypes.c_int), ("q_tiles_per_cta", ctypes.c_int), ("seq_bucket", ctypes.c_int)]
 
 
 def lib() -> ctypes.CDLL:
@@ -84,6 +90,9 @@ def lib() -> ctypes.CDLL:
         L.sage_b200_sageattn.restype = i
         L.sage_b200_sageattn.argtypes = [vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp, i, i, i, i, i, i, i,
                                          i64p, i64p, i64p, i64p, i, f, i, i, i, i, i, i, i, i, vp]
+        L.sage_b200_tile_lookup.restype = i
+        L.sage_b200_tile_lookup.argtypes = [i, i, i, i, ctypes.POINTER(TileEntry)]
+        L.sage_b200_launch_count.restype = ctypes.c_ulonglong
         L.sage_b200_set_wait_budget.restype = ctypes.c_longlong
         L.sage_b200_set_wait_budget.argtypes = [ctypes.c_longlong]
         _lib = L

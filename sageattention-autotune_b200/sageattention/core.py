@@ -305,15 +305,15 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         elif pv_accum_dtype == _FP8_PV:
             raise ValueError("smooth_v goes with pv_accum_dtype='fp16' only.")
 
-    # TMA and the vector kernels need 16-byte aligned rows (all three tensors are 16-bit: 8 elements)
-    def _aligned(t):
-        return t if (t.storage_offset() % 8 == 0 and all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
-    q, k, v = _aligned(q), _aligned(k), _aligned(v)
-
     blk_q, blk_k, warp_q, warp_k = qk_config
     if torch.compiler.is_compiling():
+        # (the operators make their own aligned copies where a tensor needs one)
         return _sageattn_traceable(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, smooth_v, return_lse,
                                    qk_config, sm_scale, qk_quant_gran, head_dim)
+    # TMA and the vector kernels need 16-byte aligned rows
+    def _aligned(t):
+        return t if (t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])) else t.contiguous()
+    q, k, v = _aligned(q), _aligned(k), _aligned(v)
     if _profile is None and not smooth_v and pv_accum_dtype in _PV_CODE:
         return _sageattn_one_call(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth_k, return_lse,
                                   qk_config, sm_scale, qk_quant_gran, head_dim)

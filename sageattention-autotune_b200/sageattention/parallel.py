@@ -40,38 +40,99 @@ def slice_heads(t: torch.Tensor, tensor_layout: str, lo: int, hi: int) -> torch.
 
 def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout: str = "HND",
                      group: Optional[dist.ProcessGroup] = None, gather: bool = True,
-                     attn_fn: Optional[Callable] = None, num_kv_heads: Optional[int] = None, **kwargs):
+                     attn_fn: Optional[Callable] = None, num_kv_heads: Optional[int] = None,
+                     gather_groups: Optional[int] = None, **kwargs):
     """Run attention on this rank's heads; optionally all-gather the full output.
 
     q_local/k_local/v_local hold only this rank's heads (as produced by `local_heads` +
-    `slice_heads`); `num_kv_heads` is the global kv-head count (defaults to num_q_heads).  With gather=True every rank returns the output for all `num_q_heads` heads,
-    in the input layout; with gather=False the local result is returned untouched and no
-    collective is issued.  `attn_fn` defaults to sageattention.sageattn."""
+    `slice_heads`); `num_kv_heads` is the global kv-head count (defaults to num_q_heads).  With
+    gather=False the local result is returned untouched and no collective is issued (a rank that
+    owns no head returns an empty tensor).  With gather=True every rank returns the output for all
+    `num_q_heads` heads in the input layout, and the collective is overlapped with the compute: the
+    local kv-heads are processed in `gather_groups` groups (default: up to 4), and while group g+1 is
+    computed on the current stream, group g is all-gathered by NCCL on a side stream.  `attn_fn`
+    defaults to sageattention.sageattn."""
     if attn_fn is None:
         from .core import sageattn as attn_fn
-    res = attn_fn(q_local, k_local, v_local, tensor_layout=tensor_layout, **kwargs)
-    if not gather or not dist.is_initialized() or dist.get_world_size(group) == 1:
-        return res
-    world = dist.get_world_size(group)
-    want_lse = isinstance(res, tuple)
-    out, lse = res if want_lse else (res, None)
     h_dim = 1 if tensor_layout == "HND" else 2
+    n_q_local, n_kv_local = q_local.size(h_dim), k_local.size(h_dim)
+    want_lse = bool(kwargs.get("return_lse"))
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if not gather or world == 1:
+        if n_kv_local == 0:                               # more ranks than kv-heads: nothing to compute here
+            empty_lse = q_local.new_empty((q_local.size(0), 0, q_local.size(3 - h_dim)), dtype=torch.float32)
+            return (q_local.new_empty(q_local.shape), empty_lse) if want_lse else q_local.new_empty(q_local.shape)
+        return attn_fn(q_local, k_local, v_local, tensor_layout=tensor_layout, **kwargs)
+
     num_kv_heads = num_q_heads if num_kv_heads is None else num_kv_heads
-    per = -(-num_kv_heads // world) * (num_q_heads // num_kv_heads)     # q-heads per rank slot
+    rep = num_q_heads // num_kv_heads
+    per_kv = -(-num_kv_heads // world)                    # kv-head slots per rank (the last ranks may fill fewer)
+    per = per_kv * rep                                    # q-head slots per rank
+    groups = max(1, min(gather_groups or 4, per_kv))
+    bounds = [(g * per_kv // groups, (g + 1) * per_kv // groups) for g in range(groups)]
+    on_gpu = q_local.is_cuda
+    # the gathered output, head-major: (world, per, *rest) with rest = the other dimensions in order
+    rest = tuple(q_local.movedim(h_dim, 0).shape[1:])
+    full = torch.empty((world, per) + rest, dtype=q_local.dtype, device=q_local.device)
+    lse_rest = (q_local.size(0), q_local.size(3 - h_dim))             # (batch, seq)
+    lse_full = torch.empty((world, per) + lse_rest, dtype=torch.float32, device=q_local.device) if want_lse else None
+    main = torch.cuda.current_stream(q_local.device) if on_gpu else None
+    side = torch.cuda.Stream(q_local.device) if on_gpu else None
 
-    def gather_heads(x, dim):
-        # equal-sized slots of `per` heads, head dim moved to the front so that each rank's
-        # contribution is one contiguous block of the gathered buffer
-        xt = x.movedim(dim, 0)
-        slot = torch.zeros((per,) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
-        slot[: xt.size(0)] = xt
-        full = torch.empty((world * per,) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(full, slot.contiguous(), group=group)
-        return full[:num_q_heads].movedim(0, dim)
+    def gather_into(dst, slot, lo, hi):
+        """all-gather `slot` ((hi - lo) head slots, head-major, contiguous) into dst[:, lo:hi] of every rank"""
+        n = hi - lo
+        if lo == 0 and hi == dst.size(1):                             # straight into the final buffer
+            dist.all_gather_into_tensor(dst.view((world * n,) + tuple(dst.shape[2:])), slot, group=group)
+        else:
+            tmp = torch.empty((world * n,) + tuple(slot.shape[1:]), dtype=slot.dtype, device=slot.device)
+            dist.all_gather_into_tensor(tmp, slot, group=group)
+            dst[:, lo:hi].copy_(tmp.view((world, n) + tuple(slot.shape[1:])))
+            if on_gpu:
+                tmp.record_stream(side)
 
-    out_full = gather_heads(out, h_dim)
+    for lo_kv, hi_kv in bounds:
+        n_here = max(0, min(hi_kv, n_kv_local) - lo_kv)               # local kv-heads that fall into this group
+        lo, hi = lo_kv * rep, hi_kv * rep
+        slot = lse_slot = None
+        if n_here > 0:
+            res = attn_fn(slice_heads(q_local, tensor_layout, lo, lo + n_here * rep),
+                          slice_heads(k_local, tensor_layout, lo_kv, lo_kv + n_here),
+                          slice_heads(v_local, tensor_layout, lo_kv, lo_kv + n_here), tensor_layout=tensor_layout, **kwargs)
+            out, lse = res if want_lse else (res, None)
+            slot = out.movedim(h_dim, 0)
+            lse_slot = lse.movedim(1, 0) if want_lse else None
+        if n_here < hi_kv - lo_kv:                                    # a ragged or empty group: pad the slots
+            pad = torch.zeros((hi - lo,) + rest, dtype=q_local.dtype, device=q_local.device)
+            if slot is not None:
+                pad[: slot.size(0)] = slot
+            slot = pad
+            if want_lse:
+                lpad = torch.zeros((hi - lo,) + lse_rest, dtype=torch.float32, device=q_local.device)
+                if lse_slot is not None:
+                    lpad[: lse_slot.size(0)] = lse_slot
+                lse_slot = lpad
+        slot = slot.contiguous()
+        if want_lse:
+            lse_slot = lse_slot.contiguous()
+        if on_gpu:
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                gather_into(full, slot, lo, hi)
+                if want_lse:
+                    gather_into(lse_full, lse_slot, lo, hi)
+            slot.record_stream(side)
+            if want_lse:
+                lse_slot.record_stream(side)
+        else:
+            gather_into(full, slot, lo, hi)
+            if want_lse:
+                gather_into(lse_full, lse_slot, lo, hi)
+    if on_gpu:
+        main.wait_stream(side)
+    out_full = full.reshape((world * per,) + rest)[:num_q_heads].movedim(0, h_dim)
     if want_lse:
-        return out_full, gather_heads(lse, 1)
+        return out_full, lse_full.reshape((world * per,) + lse_rest)[:num_q_heads].movedim(0, 1)
     return out_full
 
 

@@ -130,6 +130,39 @@ def test_torch_operators_are_registered_natively_with_fakes():
     assert v8.dtype == torch.float8_e4m3fn and vs.shape == (2, 2, 128)
 
 
+def test_public_call_traces_fullgraph_on_fake_cuda_tensors():
+    """torch.compile(fullgraph=True) traces the public call (LSE, a head_dim that needs padding, GQA) and a
+    function written against the per-operator path, using fake CUDA tensors: no GPU is touched, only the
+    operators' fake implementations run (the reference tests the same property on a GPU,
+    tests/test_sageattn_compile.py:21-31)."""
+    import sageattention
+    from torch._subclasses import FakeTensorMode
+    ns = torch.ops.sageattention_b200
+
+    def public(q, k, v):
+        o, lse = sageattention.sageattn(q, k, v, tensor_layout="NHD", is_causal=True, return_lse=True)
+        return o * 2, lse
+
+    def per_op(q, k, v):
+        km = ns.mean_k(k, 0)
+        q8, qs = ns.quant_int8(q, None, 0, 128, 32, 0, 0)
+        k8, ks = ns.quant_int8(k, km, 0, 64, 64, 1, 0)
+        o = torch.empty_like(q)
+        ns.qk_int8_sv_f16_accum_f32_attn(q8, k8, ns.cast_v_f16(v, 0), o, qs, ks, 0, True, 0.1, 128, 64, 32, 64, False)
+        return o
+
+    with FakeTensorMode():
+        q = torch.empty(1, 300, 4, 80, dtype=torch.float16, device="cuda")
+        k = torch.empty(1, 300, 2, 80, dtype=torch.float16, device="cuda")
+        o, lse = torch.compile(public, fullgraph=True, backend="eager")(q, k, k)
+        assert o.shape == q.shape and lse.shape == (1, 4, 300)
+        q2 = torch.empty(2, 256, 4, 128, dtype=torch.bfloat16, device="cuda")
+        assert torch.compile(per_op, fullgraph=True, backend="eager")(q2, q2, q2).shape == q2.shape
+        o8 = torch.compile(lambda a, b, c: sageattention.sageattn_qk_int8_pv_fp8_cuda(a, b, c, tensor_layout="NHD"),
+                           fullgraph=True, backend="eager")(q2, q2, q2)
+        assert o8.shape == q2.shape
+
+
 def test_argument_errors_do_not_need_a_gpu():
     from sageattention import _capi
     lib = _capi.lib()
@@ -159,10 +192,23 @@ def test_front_end_validation_matches_reference_errors():
 
 
 def test_tile_table_is_total_and_consistent():
-    from sageattention.tile_table import QK_CONFIGS, SUPPORTED_QK_CONFIGS, select_qk_config
+    from sageattention.tile_table import QK_CONFIGS, SUPPORTED_QK_CONFIGS, select_entry, select_qk_config
+    seen = set()
     for d in (64, 128, 256):
         for causal in (False, True):
-            for acc in ("fp32", "fp16", "fp16+fp32"):
-                for n in (1, 1024, 1025, 75600, 131072, 10 ** 6):
+            for acc in ("fp32", "fp16", "fp16+fp32", "fp8"):
+                for n in (1, 1024, 1025, 4096, 75600, 131072, 10 ** 6):
                     cfg = select_qk_config(d, causal, acc, n)
                     assert cfg in SUPPORTED_QK_CONFIGS and cfg in QK_CONFIGS
+                    e = select_entry(d, causal, acc, n)
+                    assert e["qk_config"] == cfg and e["q_tiles_per_cta"] in (1, 2)
+                    seen.add((e["kernel"], e["q_tiles_per_cta"]))
+    # the table selects among kernels: the two-level mode runs the one-tile kernel with a fold warpgroup,
+    # except at head_dim 256 where only the two-tile kernel has room; the other modes run the two-tile kernel
+    assert select_entry(128, True, "fp16+fp32", 32768)["kernel"] == "one_tile_fold"
+    assert select_entry(64, False, "fp16+fp32", 4096)["kernel"] == "one_tile_fold"
+    assert select_entry(256, True, "fp16+fp32", 4096) == {"qk_config": (128, 64, 32, 64), "kernel": "two_tile_coupled",
+                                                           "q_tiles_per_cta": 1, "seq_bucket": 2}
+    assert select_entry(128, True, "fp32", 32768)["kernel"] == "two_tile"
+    assert select_entry(128, True, "fp32", 32768)["q_tiles_per_cta"] == 2
+    assert len(seen) >= 3

@@ -30,11 +30,12 @@ def test_local_heads_keeps_gqa_groups_together():
 
 
 def _fake_attn(q, k, v, tensor_layout="HND", return_lse=False, **_):
-    # deterministic stand-in with the real call's shapes: mean of V broadcast over queries + q
+    # deterministic stand-in with the real call's shapes: first row of V broadcast over queries + q (no
+    # reduction, so the value does not depend on how the heads are grouped)
     seq = 2 if tensor_layout == "HND" else 1
     hd = 1 if tensor_layout == "HND" else 2
     rep = q.size(hd) // k.size(hd)
-    vm = v.mean(dim=seq, keepdim=True).repeat_interleave(rep, dim=hd)
+    vm = v.narrow(seq, 0, 1).repeat_interleave(rep, dim=hd)
     out = q + vm
     if return_lse:
         lse = out.float().sum(-1)
@@ -71,7 +72,8 @@ def _free_port():
     return p
 
 
-@pytest.mark.parametrize("world,layout,hq,hkv", [(2, "HND", 8, 4), (2, "NHD", 6, 3), (3, "HND", 8, 8)])
+@pytest.mark.parametrize("world,layout,hq,hkv", [(2, "HND", 8, 4), (2, "NHD", 6, 3), (3, "HND", 8, 8), (3, "HND", 4, 2),
+                                                 (2, "NHD", 16, 8)])
 def test_sharded_attention_gathers_full_output(world, layout, hq, hkv):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
