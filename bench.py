@@ -56,6 +56,28 @@ WORKLOADS = {
 }
 
 
+def bind_host_to_gpu(index: int):
+    """Pin this process to the CPUs NVML reports as local to GPU `index` before any pinned host buffer
+    is allocated, so that the buffers of the end-to-end leg land on the GPU's NUMA node (first touch)
+    whichever core the launcher happened to start the process on.  Returns a description or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        props = torch.cuda.get_device_properties(index)
+        bus_id = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = [64 * w + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1]
+        cpus = sorted(set(cpus) & os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return {"cpus": f"{cpus[0]}-{cpus[-1]} ({len(cpus)})", "source": "nvmlDeviceGetCpuAffinity"}
+    except Exception as e:  # no NVML, no permission: run where we are
+        return {"cpus": None, "source": f"unchanged ({type(e).__name__})"}
+    return None
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -235,6 +257,7 @@ def run_reference(args, w):
     if reference_gpu_available(w):
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         dev = torch.device("cuda", torch.cuda.current_device())
+        bind_host_to_gpu(dev.index)
         q, k, v = make_inputs(w, 0, w["Hkv"], dev)
         step, ev = reference_gpu_step(w)
         sampler = ClockSampler(dev.index)
@@ -304,6 +327,45 @@ def run_reference(args, w):
     print(json.dumps(line))
 
 
+def run_attn_only(args, w):
+    """The attention kernel alone, back to back, on one GPU: the measurement behind the tile table.
+    SAGE_B200_KERNEL=coupled selects the candidate the table does not."""
+    from sageattention import quant
+    from sageattention.core import attn_fwd_quantized
+    from sageattention.tile_table import select_entry
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    q, k, v = make_inputs(w, 0, w["Hkv"], dev)
+    layout = w["layout"]
+    entry = select_entry(w["D"], w["causal"], w["pv"], w["N"])
+    cfg = entry["qk_config"]
+    km = quant.mean_k(k, layout)
+    q8, qs, k8, ks = quant.per_thread_int8(q, k, km, cfg[0], cfg[2], cfg[1], cfg[3], layout)
+    v_scale = None
+    if w["pv"] == "fp8":
+        v16, v_scale = quant.quant_v_fp8(v, layout)
+    else:
+        v16 = quant.cast_v_fp16(v, layout)
+    out = torch.empty_like(q)
+    mode = "fp32" if w["pv"] == "fp8" else w["pv"]
+
+    def run():
+        attn_fwd_quantized(q8, k8, v16, out, qs, ks, layout, w["causal"], w["D"] ** -0.5, cfg, mode, False, "per_thread", v_scale)
+    for _ in range(max(3, args.warmup)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    executed = literal_flops(w, w["Hq"]) * (0.5 if w["causal"] else 1.0)
+    print(json.dumps({"attn_only": args.workload, "ms": ms, "executed_tflops": executed / (ms * 1e-3) / 1e12,
+                      "table_entry": entry, "kernel_override": os.environ.get("SAGE_B200_KERNEL"), "steps": args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -315,10 +377,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-gather", action="store_true", help="skip the second timed loop with the NCCL all-gather")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels after the run")
+    ap.add_argument("--attn-only", action="store_true",
+                    help="time the attention kernel alone on pre-quantised inputs (tile-table sweeps) and print one line")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
+        return
+    if args.attn_only:
+        run_attn_only(args, w)
         return
 
     import torch.distributed as dist
@@ -334,6 +401,7 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    host_binding = bind_host_to_gpu(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     (q_lo, q_hi), (kv_lo, kv_hi) = local_heads(w["Hq"], w["Hkv"], world, rank)
@@ -455,7 +523,7 @@ def main():
                 "config": {"workload": args.workload, **{k_: w[k_] for k_ in ("B", "Hq", "Hkv", "N", "D", "causal", "pv", "layout")},
                            "in_dtype": w["dtype"], "sharding": f"kv-heads over {world} rank(s), no collective in the timed region",
                            "l2": "inputs (1.6 GB per step at N=32k) exceed the 126 MB L2; no flush needed"},
-                "executed_tops": value * (0.5 if w["causal"] else 1.0),
+                "executed_tops": value * (0.5 if w["causal"] else 1.0), "host_binding": host_binding,
                 "clocks": clocks, "roofline": roofline, "e2e": e2e,
                 "gpu_launches": int(launches) * world,
                 "gpu_launches_note": "kernels of libsage_b200.so launched inside the timed region, counted by the library "

@@ -54,13 +54,6 @@ static int make_map(CUtensorMap* map, const void* base, int elem_bytes, int batc
   return SAGE_B200_OK;
 }
 
-// Environment overrides of the tile table, for sweeps: SAGE_B200_KERNEL=coupled runs the two-level mode on
-// the two-tile kernel, SAGE_B200_QTILES=1|2 fixes the query tiles per CTA of the two-tile kernel.
-static int env_int(const char* name) {
-  const char* e = getenv(name);
-  return (e != nullptr && e[0] >= '0' && e[0] <= '9') ? atoi(e) : -1;
-}
-
 template <int D, int PV_MODE, int OUT_DTYPE, int KSUB>
 static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
                        cudaStream_t stream) {
@@ -75,14 +68,13 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   int threads = kAttnThreads;
   int which = 0;               // index of the kernel in the per-device attribute cache below
   sage_b200_tile_entry te = tile_lookup(D, p.causal, PV_MODE, p.len_kv);
+  // SAGE_B200_KERNEL=coupled overrides the table for sweeps and cross-checks: the two-level mode on the
+  // two-tile kernel
   static const bool force_coupled = [] {
     const char* e = getenv("SAGE_B200_KERNEL");
     return e != nullptr && e[0] == 'c';
   }();
-  static const int force_tiles = env_int("SAGE_B200_QTILES");
-  if (force_coupled && te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD) te.kernel = SAGE_B200_KERNEL_TWO_TILE_COUPLED, te.q_tiles_per_cta = 2;
-  if ((force_tiles == 1 || force_tiles == 2) && te.kernel != SAGE_B200_KERNEL_ONE_TILE_FOLD && D != 256)
-    te.q_tiles_per_cta = force_tiles;
+  if (force_coupled && te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD) te.kernel = SAGE_B200_KERNEL_TWO_TILE_COUPLED;
   bool one_tile_fold = false;
   if constexpr (PV_MODE == SAGE_B200_PV_F16_F32 && D != 256 && KSUB == 1) {
     one_tile_fold = (te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD);
@@ -94,24 +86,16 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     }
   }
   constexpr bool kFp8 = (PV_MODE == SAGE_B200_PV_F8);
-  // (an entry that names the one-tile kernel for a configuration only the two-tile kernel is built for
-  // falls back to two tiles per CTA)
-  const int tiles = (one_tile_fold || D == 256) ? 1 : (te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD ? 2 : te.q_tiles_per_cta);
   if (!one_tile_fold) {
-    if (tiles == 1 && D != 256) {
-      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB, 1>;
-      smem = v1::SmemPlan<D, kFp8, 1>::kDynamic;
-      which = 2;
-    } else {
-      kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB, 2>;
-      smem = v1::SmemPlan<D, kFp8, 2>::kDynamic;
-    }
+    kern = v1::sage_attn_fwd_kernel<D, PV_MODE, OUT_DTYPE, KSUB>;
+    smem = v1::SmemPlan<D, kFp8>::kDynamic;
   }
+  const int tiles = (one_tile_fold || D == 256) ? 1 : 2;
   const int rows_per_cta = tiles * kTileQ;
   const dim3 grid((p.len_q + rows_per_cta - 1) / rows_per_cta, p.heads_q, p.batch);
   cudaError_t attr_err = cudaSuccess;
   // the attribute is per device: set it for every device that launches
-  static bool done[3][64] = {};
+  static bool done[2][64] = {};
   static std::mutex mu;
   int dev = 0;
   SAGE_CUDA_TRY(cudaGetDevice(&dev));

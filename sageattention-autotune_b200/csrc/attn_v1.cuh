@@ -52,12 +52,11 @@ enum BarIdx {
 
 // head_dim 256 runs this kernel with ONE query tile per CTA (S + a 256-column O fill tensor memory
 // for one tile only) and two K/V stages instead of three (Q 32 KB + 2 x 32 KB + 2 x 64 KB = 224 KB).
-// TILES = 1 selects one query tile per CTA for the smaller head dims too: twice the CTAs, each K/V
-// block fetched per 128 instead of 256 query rows; the tile table picks it where a launch is too small
-// to fill the GPU with 256-row CTAs.
-template <int D, bool F8 = false, int TILES = 2>
+// (One tile per CTA for the smaller head dims as well was measured and dropped: twice the CTAs, but each
+// K/V block fetched per 128 instead of 256 query rows; 20-60 % slower from N = 1024 to 16384, causal or not.)
+template <int D, bool F8 = false>
 struct SmemPlan {
-  static constexpr int kTiles = (D == 256) ? 1 : TILES;
+  static constexpr int kTiles = (D == 256) ? 1 : 2;
   static constexpr int kStagesK = (D == 256) ? 2 : kKStages;
   static constexpr int kStagesV = (D == 256) ? 2 : kVStages;
   static constexpr int kQBytes = kTileQ * D;                 // int8
@@ -460,12 +459,12 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
   ptx::tc_fence_before();
 }
 
-template <int D, int PV_MODE, int OUT_DTYPE, int KSUB = 1, int TILES = 2>
+template <int D, int PV_MODE, int OUT_DTYPE, int KSUB = 1>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   constexpr bool kFp8 = (PV_MODE == SAGE_B200_PV_F8);
-  using Plan = SmemPlan<D, kFp8, TILES>;
+  using Plan = SmemPlan<D, kFp8>;
   constexpr bool kF16Acc = (PV_MODE == SAGE_B200_PV_F16);
   constexpr bool kInstBuf = (PV_MODE == SAGE_B200_PV_F16_F32);
   extern __shared__ uint8_t smem_raw[];

@@ -299,35 +299,25 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
     const float alpha = (r_out == r_new) ? 1.0f : pow2_int(fmaxf(r_out - r_new, -127.0f));
     const float beta = (r_blk == r_new) ? 1.0f : pow2_int(fmaxf(r_blk - r_new, -127.0f));
     r_out = r_new;
-    // T is read 64 channels at a time, two fp16 values per register.  Three cases, decided per warp: both
-    // factors are 1 (a plain mixed-precision add: 95 % of the blocks at N = 32768), only this block is
-    // scaled (its reference lies below the output's: one mixed-precision FMA), or the output moves too.
-    const bool any_alpha = __any_sync(0xffffffffu, alpha != 1.0f);
-    const bool any_beta = __any_sync(0xffffffffu, beta != 1.0f);
-    const uint32_t beta16 = __half_as_ushort(__float2half_rn(beta));       // exact, or 0 below 2^-24
+    const bool plain = !__any_sync(0xffffffffu, alpha != 1.0f || beta != 1.0f);
+    if (plain) {
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 64) {
-      uint32_t t16[32];
-      ptx::tmem_ld32_pack16<0>(t_src + c0, t16);
-      ptx::tmem_wait_ld();
-      if (!any_alpha && !any_beta) {
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t t16[32];
+        ptx::tmem_ld32<0>(t_src + c0, t16);
+        ptx::tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o[c0 + 2 * i] = ptx::add_f32_f16half<0>(o[c0 + 2 * i], t16[i]);
-          o[c0 + 2 * i + 1] = ptx::add_f32_f16half<1>(o[c0 + 2 * i + 1], t16[i]);
-        }
-      } else if (!any_alpha) {
+        for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::add_f32_f16lo(o[c0 + i], t16[i]);
+      }
+    } else {
+      const uint32_t beta16 = __half_as_ushort(__float2half_rn(beta));     // exact, or 0 below 2^-24
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o[c0 + 2 * i] = ptx::fma_f32_f16half<0>(t16[i], beta16, o[c0 + 2 * i]);
-          o[c0 + 2 * i + 1] = ptx::fma_f32_f16half<1>(t16[i], beta16, o[c0 + 2 * i + 1]);
-        }
-      } else {
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t t16[32];
+        ptx::tmem_ld32<0>(t_src + c0, t16);
+        ptx::tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o[c0 + 2 * i] = ptx::fma_f32_f16half<0>(t16[i], beta16, o[c0 + 2 * i] * alpha);
-          o[c0 + 2 * i + 1] = ptx::fma_f32_f16half<1>(t16[i], beta16, o[c0 + 2 * i + 1] * alpha);
-        }
+        for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::fma_f32_f16lo(t16[i], beta16, o[c0 + i] * alpha);
       }
     }
     ptx::tc_fence_before();

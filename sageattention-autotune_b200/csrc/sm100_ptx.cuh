@@ -72,31 +72,18 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// `tries` attempts in a loop that issues nothing else: four attempts per counter update
-__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, uint32_t tries) {
+// the same with a suspend-time hint: the hardware may park the thread for up to `ns` nanoseconds
+// (or until the phase completes) before the instruction returns
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
   uint32_t ok;
   asm volatile(
       "{\n"
-      " .reg .pred p, q;\n"
-      " .reg .u32 n;\n"
-      " mov.u32 n, %3;\n"
-      "SAGE_SPIN:\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " @p bra SAGE_SPIN_DONE;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " @p bra SAGE_SPIN_DONE;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " @p bra SAGE_SPIN_DONE;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " @p bra SAGE_SPIN_DONE;\n"
-      " sub.u32 n, n, 4;\n"
-      " setp.gt.s32 q, n, 0;\n"
-      " @q bra SAGE_SPIN;\n"
-      "SAGE_SPIN_DONE:\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       " selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(tries)
+      : "r"(bar), "r"(parity), "r"(ns)
       : "memory");
   return ok != 0;
 }
@@ -214,19 +201,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[N]) {
       : "r"(taddr)
       : "memory");
 }
-// The same for 16-bit data held one value per 32-bit column (an fp16 accumulator): 64 consecutive
-// columns, two per register (the lower column in the low half)
-template <int OFF, int N>
-__device__ __forceinline__ void tmem_ld32_pack16(uint32_t taddr, uint32_t (&r)[N]) {
-  static_assert(OFF + 32 <= N, "register window out of range");
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.pack::16b.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : SAGE_R32(r, OFF)
-      : "r"(taddr)
-      : "memory");
-}
 template <int OFF, int N>
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[N]) {
   static_assert(OFF + 32 <= N, "register window out of range");
@@ -337,29 +311,6 @@ __device__ __forceinline__ float add_f32_f16lo(float acc, uint32_t packed) {
       "}"
       : "=f"(r)
       : "r"(packed), "f"(acc));
-  return r;
-}
-// the same on either half of a register that packs two fp16 values
-template <int HI>
-__device__ __forceinline__ float add_f32_f16half(float acc, uint32_t packed) {
-  float r;
-  if constexpr (HI) {
-    asm("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %1;\n add.rn.f32.f16 %0, hi, %2;\n}" : "=f"(r) : "r"(packed), "f"(acc));
-  } else {
-    asm("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %1;\n add.rn.f32.f16 %0, lo, %2;\n}" : "=f"(r) : "r"(packed), "f"(acc));
-  }
-  return r;
-}
-template <int HI>
-__device__ __forceinline__ float fma_f32_f16half(uint32_t packed, uint32_t b16, float acc) {
-  float r;
-  if constexpr (HI) {
-    asm("{\n .reg .b16 lo, hi, bl, bh;\n mov.b32 {lo, hi}, %1;\n mov.b32 {bl, bh}, %2;\n fma.rn.f32.f16 %0, hi, bl, %3;\n}"
-        : "=f"(r) : "r"(packed), "r"(b16), "f"(acc));
-  } else {
-    asm("{\n .reg .b16 lo, hi, bl, bh;\n mov.b32 {lo, hi}, %1;\n mov.b32 {bl, bh}, %2;\n fma.rn.f32.f16 %0, lo, bl, %3;\n}"
-        : "=f"(r) : "r"(packed), "r"(b16), "f"(acc));
-  }
   return r;
 }
 // three-input maximum

@@ -12,8 +12,9 @@
 //   * the kernel: the two-tile kernel (attn_v1.cuh), the one-tile kernel with a fold warpgroup
 //     (attn_v4.cuh, the two-level "fp16+fp32" accumulation only), or the two-tile kernel folding
 //     inside its softmax warps ("coupled": head_dim 256 and 32-key scale blocks in that mode);
-//   * for the two-tile kernel, how many 128-row query tiles one CTA takes (2, or 1 where 256-row
-//     CTAs are too few to keep 148 SMs busy).
+//   * how many 128-row query tiles one CTA takes: 1 for the one-tile kernel and for head_dim 256, else 2.
+//     (One tile per CTA on the two-tile kernel was measured as a candidate for short sequences and
+//     lost everywhere, so no entry selects it.)
 // Keys: head_dim (64 / 128 / 256 after padding), causal, accumulate mode, and a bucket of the key
 // length.  The measurements behind the entries are summarised in profiles/tile_table_sweep.md.
 #pragma once
@@ -24,11 +25,6 @@ namespace sage {
 
 constexpr int kSeqBucketEdges[] = {1024, 2048, 4096, 16384, 65536};
 constexpr int kSeqBuckets = 6;
-
-// Two-tile kernel: largest bucket that runs with one query tile per CTA (-1: none).  Separate values for
-// causal and full attention: a causal launch has half the work per CTA on average.
-constexpr int kOneTileMaxBucketCausal = -1;
-constexpr int kOneTileMaxBucketFull = -1;
 
 inline int seq_bucket(int len_kv) {
   for (int i = 0; i < kSeqBuckets - 1; ++i)
@@ -49,10 +45,14 @@ inline sage_b200_tile_entry tile_lookup(int head_dim, int is_causal, int pv_accu
     e.q_tiles_per_cta = 1;
   } else {
     e.kernel = (pv_accum == SAGE_B200_PV_F16_F32) ? SAGE_B200_KERNEL_TWO_TILE_COUPLED : SAGE_B200_KERNEL_TWO_TILE;
-    // one query tile per CTA for short sequences (entries from the sweep: see the summary file)
-    const int one_tile_max = is_causal ? kOneTileMaxBucketCausal : kOneTileMaxBucketFull;
-    e.q_tiles_per_cta = (head_dim == 256 || bucket <= one_tile_max) ? 1 : 2;
+    // two-tile kernel, two query tiles per CTA against one, kernel time in ms on B200 (fp32 mode):
+    //   D 128 causal H 64:  N 1024  0.044 / 0.053   N 2048  0.110 / 0.144   N 4096  0.312 / 0.447   N 16384  3.51 / 5.73
+    //   D 128 full   H 64:  N 1024  0.046 / 0.067   N 2048  0.147 / 0.207   N 4096  0.460 / 0.747
+    //   D  64 full B 16 H 10:  N 1024  0.098 / 0.127   N 2048  0.311 / 0.440   N 4096  1.145 / 1.602
+    //   D 128 H 8 N 4096 (a launch of 128 CTAs):  causal 0.069 / 0.084   full 0.071 / 0.110
+    e.q_tiles_per_cta = (head_dim == 256) ? 1 : 2;
   }
+  (void)is_causal;
   return e;
 }
 
