@@ -62,6 +62,7 @@ extern "C" {
 #define SAGE_B200_KERNEL_TWO_TILE         0  /* 256 query rows per CTA share every K/V block; O accumulates in tensor memory */
 #define SAGE_B200_KERNEL_ONE_TILE_FOLD    1  /* 128 query rows per CTA, fp16 partial products folded into fp32 by a fold warpgroup */
 #define SAGE_B200_KERNEL_TWO_TILE_COUPLED 2  /* the two-level mode inside the two-tile kernel's softmax warps */
+#define SAGE_B200_KERNEL_ONE_TILE_PERSISTENT 3  /* the one-tile kernel as one CTA per SM walking over the query tiles */
 
 /*
  * One entry of the fixed tile table.  Replaces the reference's run-time selection among

@@ -22,7 +22,10 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "sageattention", "libsage_b200.so")
 TORCH_LIB = os.path.join(HERE, "sageattention", "libsage_b200_torch.so")
-CXX = os.environ.get("CXX", "g++")
+# Host compiler of the operator library.  Deliberately not $CXX: the library must share the C++ run time
+# (libstdc++.so) with torch, and a relocated toolchain that only ships libstdc++.a links a private
+# copy in, after which an exception thrown by an operator kills the process instead of reaching Python.
+CXX = os.environ.get("SAGE_B200_CXX", "g++")
 SOURCES = ["api.cu", "quant.cu", "attn_fwd.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -79,6 +82,11 @@ def build_torch_ops(force: bool = False) -> str:
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("g++ failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    syms = subprocess.run(["nm", "-D", "--defined-only", TORCH_LIB], capture_output=True, text=True).stdout
+    if " __cxa_throw" in syms:
+        os.remove(TORCH_LIB)
+        raise RuntimeError(f"{CXX} linked a private copy of the C++ run time into the operator library; "
+                           "set SAGE_B200_CXX to a g++ that links libstdc++.so")
     return TORCH_LIB
 
 

@@ -8,6 +8,7 @@
 #include "attn_common.cuh"
 #include "attn_v1.cuh"
 #include "attn_v4.cuh"
+#include "attn_v5.cuh"
 #include "tile_table.h"
 
 namespace sage {
@@ -75,14 +76,26 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     return e != nullptr && e[0] == 'c';
   }();
   if (force_coupled && te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD) te.kernel = SAGE_B200_KERNEL_TWO_TILE_COUPLED;
-  bool one_tile_fold = false;
+  // SAGE_B200_KERNEL=persistent / =plain force the persistent or the one-CTA-per-tile form of the one-tile kernel
+  static const int force_persistent = [] {
+    const char* e = getenv("SAGE_B200_KERNEL");
+    return (e != nullptr && e[0] == 'p' && e[1] == 'e') ? 1 : (e != nullptr && e[0] == 'p' && e[1] == 'l') ? 0 : -1;
+  }();
+  bool one_tile_fold = false, persistent = false;
   if constexpr (PV_MODE == SAGE_B200_PV_F16_F32 && D != 256 && KSUB == 1) {
-    one_tile_fold = (te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD);
+    one_tile_fold = (te.kernel == SAGE_B200_KERNEL_ONE_TILE_FOLD || te.kernel == SAGE_B200_KERNEL_ONE_TILE_PERSISTENT);
     if (one_tile_fold) {
-      kern = v4::sage_attn_fwd_kernel<D, OUT_DTYPE>;
-      smem = v4::SmemPlan<D>::kDynamic;
+      persistent = force_persistent >= 0 ? force_persistent == 1 : te.kernel == SAGE_B200_KERNEL_ONE_TILE_PERSISTENT;
+      if (persistent) {
+        kern = v5::sage_attn_fwd_kernel<D, OUT_DTYPE>;
+        smem = v5::SmemPlan<D>::kDynamic;
+        which = 2;
+      } else {
+        kern = v4::sage_attn_fwd_kernel<D, OUT_DTYPE>;
+        smem = v4::SmemPlan<D>::kDynamic;
+        which = 1;
+      }
       threads = v4::kThreads;
-      which = 1;
     }
   }
   constexpr bool kFp8 = (PV_MODE == SAGE_B200_PV_F8);
@@ -92,10 +105,11 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   }
   const int tiles = (one_tile_fold || D == 256) ? 1 : 2;
   const int rows_per_cta = tiles * kTileQ;
-  const dim3 grid((p.len_q + rows_per_cta - 1) / rows_per_cta, p.heads_q, p.batch);
+  dim3 grid((p.len_q + rows_per_cta - 1) / rows_per_cta, p.heads_q, p.batch);
   cudaError_t attr_err = cudaSuccess;
   // the attribute is per device: set it for every device that launches
-  static bool done[2][64] = {};
+  static bool done[3][64] = {};
+  static int sm_count[64] = {};
   static std::mutex mu;
   int dev = 0;
   SAGE_CUDA_TRY(cudaGetDevice(&dev));
@@ -107,6 +121,20 @@ static int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
         return fail(SAGE_B200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", smem, cudaGetErrorString(attr_err));
       if (dev >= 0 && dev < 64) done[which][dev] = true;
     }
+  }
+  if (persistent) {
+    // one CTA per SM walks over the query tiles of all heads
+    int sms = 0;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      if (dev >= 0 && dev < 64 && sm_count[dev] == 0)
+        SAGE_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
+      sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
+    }
+    if (sms <= 0) SAGE_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long items = static_cast<long long>(grid.x) * grid.y * grid.z;
+    SAGE_REQUIRE(items < (1ll << 31), "attn_fwd: too many query tiles for one launch");
+    grid = dim3(static_cast<unsigned>(items < sms ? items : sms), 1, 1);
   }
   SAGE_CUDA_TRY(launch_kernel(kern, grid, dim3(threads), smem, stream, mq, mk, mv, p));
   return SAGE_B200_OK;

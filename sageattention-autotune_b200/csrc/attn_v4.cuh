@@ -90,6 +90,136 @@ __device__ __forceinline__ float pow2_int(float k) {
   return __int_as_float(e << 23);
 }
 
+// One block of the softmax for one query row (thread): the scores of buffer t_s (this thread's lane) become
+// P in place, `ref` and `d_sum` (this warpgroup's reference exponent and row sum) are brought up to date,
+// and the block's reference is published for the fold warps and the other warpgroup.  `a` are the eight
+// dequantisation constants of the block, `r_other` the other warpgroup's reference of three blocks
+// earlier (or -inf), `lim` the last visible column when `need_mask`.  The caller waits for the scores
+// before and signals P after.
+__device__ __forceinline__ void softmax_block(uint32_t t_s, const float (&a)[8], bool need_mask, int lim, float r_other,
+                                              float& ref, float& d_sum, float* ref_ring_slot,
+                                              volatile float* ref_pub_slot) {
+  // pass 1: the block maximum, 64 columns at a time (the scores stay in tensor memory and are read
+  // again in pass 2: holding all 128 would cost the registers the fold warps need for O)
+  float m_blk = -INFINITY;
+#pragma unroll 1
+  for (int hf = 0; hf < 2; ++hf) {
+    uint32_t s[64];
+    ptx::tmem_ld32<0>(t_s + hf * 64, s);
+    ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
+    ptx::tmem_wait_ld();
+    if (!need_mask) {
+      // per scale class: integer maximum (three-input), then one conversion and one multiply
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {                       // the class owns columns 2t + 8i, 2t + 8i + 1
+        int v[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[2 * i] = static_cast<int>(s[2 * t + 8 * i]);
+          v[2 * i + 1] = static_cast<int>(s[2 * t + 8 * i + 1]);
+        }
+        int mx = v[0];
+#pragma unroll
+        for (int i = 1; i < 15; i += 2) mx = __vimax3_s32(mx, v[i], v[i + 1]);
+        mx = max(mx, v[15]);
+        const float at = hf ? a[4 + t] : a[t];
+        m_blk = fmaxf(m_blk, static_cast<float>(mx) * at);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
+        const float x = static_cast<float>(static_cast<int>(s[c])) * at;
+        m_blk = fmaxf(m_blk, (hf * 64 + c <= lim) ? x : -INFINITY);
+      }
+    }
+  }
+
+  // new reference: integer, at least this block's maximum, never below anything already used, and
+  // not below the other warpgroup's reference of block j-3.  That block's softmax finished before
+  // the scores of block j could be issued, so the value is always the same one: results do not depend
+  // on how the two warpgroups happen to interleave.
+  // (references move in steps of kRefStep: coarse enough that the two warpgroups nearly always agree
+  // and the fold stays a plain add, fine enough that P keeps its fp16 precision: P's largest value in
+  // a row is at least 2^-kRefStep)
+  const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk * (1.0f / kRefStep)) * kRefStep), r_other);
+  // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
+  const float m_ref = (r_new == -INFINITY) ? 0.0f : r_new;
+  const float shrink = (ref == r_new) ? 1.0f : pow2_int(fmaxf(ref - m_ref, -127.0f));
+  ref = r_new;
+  *ref_pub_slot = r_new;
+  *ref_ring_slot = r_new;         // (slot reuse: the block eight before was folded, and read by the other warpgroup, long ago)
+
+  // pass 2: P = 2^(S*a - ref), packed to fp16 pairs; the P of keys [64 hf, 64 hf + 64) overwrites
+  // score columns [32 hf, 32 hf + 32), which pass 2 has already consumed
+  float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+  // Share of 2^x evaluated with a polynomial on the FMA pipe instead of ex2.approx.  Here 0 is best
+  // (N = 32768 causal, sustained: 18.1 ms with 0/8, 18.4 with 1/8, 18.9 with 2/8, 19.6 with 3/8): with
+  // two warpgroups out of phase the special-function unit is not the limiter and the extra
+  // instructions only cost power.  The two-tile kernel (attn_v1.cuh) is issue-bound and keeps 3/8.
+#ifndef SAGE_V4_POLY
+#define SAGE_V4_POLY 0
+#endif
+  constexpr int kPolyDen = 8, kPolyNum = SAGE_V4_POLY;
+#pragma unroll 1
+  for (int hf = 0; hf < 2; ++hf) {
+    uint32_t s[64];
+    ptx::tmem_ld32<0>(t_s + hf * 64, s);
+    ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
+    ptx::tmem_wait_ld();
+    if (!need_mask) {
+      // X = float(S) + 1.5*2^23 without a conversion (|S| < 2^22), then p = 2^(X*a + neg) with
+      // neg = -(1.5*2^23*a + ref); two columns of one class per packed FMA
+      unsigned long long a2[4], neg2[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float at = hf ? a[4 + t] : a[t];
+        const float ng = fmaf(-kMagicF, at, -m_ref);
+        a2[t] = ptx::pack2(at, at);
+        neg2[t] = ptx::pack2(ng, ng);
+      }
+      unsigned long long acc0 = ptx::pack2(sum0, sum1), acc1 = ptx::pack2(sum2, sum3);
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+        const unsigned long long e0 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 0] + kMagicI), __uint_as_float(s[c + 1] + kMagicI)),
+                                                a2[(c & 7) >> 1], neg2[(c & 7) >> 1]);
+        const unsigned long long e1 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 2] + kMagicI), __uint_as_float(s[c + 3] + kMagicI)),
+                                                a2[((c + 2) & 7) >> 1], neg2[((c + 2) & 7) >> 1]);
+        float p0, p1, p2, p3;
+        if (((c >> 2) % kPolyDen) < kPolyNum) {
+          ptx::exp2_pair_poly(e0, p0, p1);
+          ptx::exp2_pair_poly(e1, p2, p3);
+        } else {
+          float x0, x1, x2, x3;
+          ptx::unpack2(e0, x0, x1);
+          ptx::unpack2(e1, x2, x3);
+          p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
+        }
+        acc0 = ptx::add2(acc0, ptx::pack2(p0, p1));
+        acc1 = ptx::add2(acc1, ptx::pack2(p2, p3));
+        s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
+        s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
+      }
+      ptx::unpack2(acc0, sum0, sum1);
+      ptx::unpack2(acc1, sum2, sum3);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
+        const float x0 = static_cast<float>(static_cast<int>(s[c + 0])) * at;
+        const float x1 = static_cast<float>(static_cast<int>(s[c + 1])) * at;
+        const float p0 = (hf * 64 + c <= lim) ? ptx::ex2(x0 - m_ref) : 0.0f;
+        const float p1 = (hf * 64 + c + 1 <= lim) ? ptx::ex2(x1 - m_ref) : 0.0f;
+        sum0 += p0;
+        sum1 += p1;
+        s[c / 2] = ptx::pack_f16x2(p0, p1);
+      }
+    }
+    ptx::tmem_st32<0>(t_s + hf * 32, s);
+  }
+  d_sum = d_sum * shrink + ((sum0 + sum1) + (sum2 + sum3));
+}
+
 // ---------------------------------------------------------------------------------------------------
 // softmax warpgroup `wg`: blocks wg, wg + 2, ... ; thread = query row, all 128 keys of a block
 // ---------------------------------------------------------------------------------------------------
@@ -132,126 +262,9 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     const bool need_mask = (k0 + kBlockKV > p.len_kv) || (p.causal && (k0 + kBlockKV - 1 > q_row0));
     const int lim = min(p.causal ? (q_row - k0) : kBlockKV, p.len_kv - k0 - 1);   // columns <= lim are visible
 
-    // pass 1: the block maximum, 64 columns at a time (the scores stay in tensor memory and are read
-    // again in pass 2: holding all 128 would cost the registers the fold warps need for O)
-    float m_blk = -INFINITY;
-#pragma unroll 1
-    for (int hf = 0; hf < 2; ++hf) {
-      uint32_t s[64];
-      ptx::tmem_ld32<0>(t_s + hf * 64, s);
-      ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
-      ptx::tmem_wait_ld();
-      if (!need_mask) {
-        // per scale class: integer maximum (three-input), then one conversion and one multiply
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {                       // the class owns columns 2t + 8i, 2t + 8i + 1
-          int v[16];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            v[2 * i] = static_cast<int>(s[2 * t + 8 * i]);
-            v[2 * i + 1] = static_cast<int>(s[2 * t + 8 * i + 1]);
-          }
-          int mx = v[0];
-#pragma unroll
-          for (int i = 1; i < 15; i += 2) mx = __vimax3_s32(mx, v[i], v[i + 1]);
-          mx = max(mx, v[15]);
-          const float at = hf ? a[4 + t] : a[t];
-          m_blk = fmaxf(m_blk, static_cast<float>(mx) * at);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
-          const float x = static_cast<float>(static_cast<int>(s[c])) * at;
-          m_blk = fmaxf(m_blk, (hf * 64 + c <= lim) ? x : -INFINITY);
-        }
-      }
-    }
-
-    // new reference: integer, at least this block's maximum, never below anything already used, and
-    // not below the other warpgroup's reference of block j-3.  That block's softmax finished before
-    // the scores of block j could be issued, so the value is always the same one: results do not depend
-    // on how the two warpgroups happen to interleave.
     const float r_other = (j >= 3) ? ref_ring[((j - 3) % kRefRing) * kTileQ + row] : -INFINITY;
-    // (references move in steps of kRefStep: coarse enough that the two warpgroups nearly always agree
-    // and the fold stays a plain add, fine enough that P keeps its fp16 precision: P's largest value in
-    // a row is at least 2^-kRefStep)
-    const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk * (1.0f / kRefStep)) * kRefStep), r_other);
-    // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
-    const float m_ref = (r_new == -INFINITY) ? 0.0f : r_new;
-    const float shrink = (ref == r_new) ? 1.0f : pow2_int(fmaxf(ref - m_ref, -127.0f));
-    ref = r_new;
-    ref_pub[wg * kTileQ + row] = r_new;
-    ref_ring[(j % kRefRing) * kTileQ + row] = r_new;      // (slot reuse: block j-8 was folded, and read by block j-5, long ago)
-
-    // pass 2: P = 2^(S*a - ref), packed to fp16 pairs; the P of keys [64 hf, 64 hf + 64) overwrites
-    // score columns [32 hf, 32 hf + 32), which pass 2 has already consumed
-    float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
-    // Share of 2^x evaluated with a polynomial on the FMA pipe instead of ex2.approx.  Here 0 is best
-    // (N = 32768 causal, sustained: 18.1 ms with 0/8, 18.4 with 1/8, 18.9 with 2/8, 19.6 with 3/8): with
-    // two warpgroups out of phase the special-function unit is not the limiter and the extra
-    // instructions only cost power.  The two-tile kernel (attn_v1.cuh) is issue-bound and keeps 3/8.
-#ifndef SAGE_V4_POLY
-#define SAGE_V4_POLY 0
-#endif
-    constexpr int kPolyDen = 8, kPolyNum = SAGE_V4_POLY;
-#pragma unroll 1
-    for (int hf = 0; hf < 2; ++hf) {
-      uint32_t s[64];
-      ptx::tmem_ld32<0>(t_s + hf * 64, s);
-      ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
-      ptx::tmem_wait_ld();
-      if (!need_mask) {
-        // X = float(S) + 1.5*2^23 without a conversion (|S| < 2^22), then p = 2^(X*a + neg) with
-        // neg = -(1.5*2^23*a + ref); two columns of one class per packed FMA
-        unsigned long long a2[4], neg2[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float at = hf ? a[4 + t] : a[t];
-          const float ng = fmaf(-kMagicF, at, -m_ref);
-          a2[t] = ptx::pack2(at, at);
-          neg2[t] = ptx::pack2(ng, ng);
-        }
-        unsigned long long acc0 = ptx::pack2(sum0, sum1), acc1 = ptx::pack2(sum2, sum3);
-#pragma unroll
-        for (int c = 0; c < 64; c += 4) {
-          const unsigned long long e0 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 0] + kMagicI), __uint_as_float(s[c + 1] + kMagicI)),
-                                                  a2[(c & 7) >> 1], neg2[(c & 7) >> 1]);
-          const unsigned long long e1 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 2] + kMagicI), __uint_as_float(s[c + 3] + kMagicI)),
-                                                  a2[((c + 2) & 7) >> 1], neg2[((c + 2) & 7) >> 1]);
-          float p0, p1, p2, p3;
-          if (((c >> 2) % kPolyDen) < kPolyNum) {
-            ptx::exp2_pair_poly(e0, p0, p1);
-            ptx::exp2_pair_poly(e1, p2, p3);
-          } else {
-            float x0, x1, x2, x3;
-            ptx::unpack2(e0, x0, x1);
-            ptx::unpack2(e1, x2, x3);
-            p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
-          }
-          acc0 = ptx::add2(acc0, ptx::pack2(p0, p1));
-          acc1 = ptx::add2(acc1, ptx::pack2(p2, p3));
-          s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
-          s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
-        }
-        ptx::unpack2(acc0, sum0, sum1);
-        ptx::unpack2(acc1, sum2, sum3);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
-          const float x0 = static_cast<float>(static_cast<int>(s[c + 0])) * at;
-          const float x1 = static_cast<float>(static_cast<int>(s[c + 1])) * at;
-          const float p0 = (hf * 64 + c <= lim) ? ptx::ex2(x0 - m_ref) : 0.0f;
-          const float p1 = (hf * 64 + c + 1 <= lim) ? ptx::ex2(x1 - m_ref) : 0.0f;
-          sum0 += p0;
-          sum1 += p1;
-          s[c / 2] = ptx::pack_f16x2(p0, p1);
-        }
-      }
-      ptx::tmem_st32<0>(t_s + hf * 32, s);
-    }
-    d_sum = d_sum * shrink + ((sum0 + sum1) + (sum2 + sum3));
+    softmax_block(t_s, a, need_mask, lim, r_other, ref, d_sum, ref_ring + (j % kRefRing) * kTileQ + row,
+                  ref_pub + wg * kTileQ + row);
     ptx::tmem_wait_st();
     ptx::tc_fence_before();
     ptx::mbar_arrive(bars + 8 * (kBarPFull + buf));       // also publishes ref_ring (release)
@@ -270,6 +283,39 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
     if (ok && got && n_blocks > 0 && p.lse != nullptr && q_row < p.len_q)
       p.lse[(static_cast<int64_t>(b) * p.heads_q + h) * p.len_q + q_row] = ptx::lg2(total) + r_fin;
     ptx::mbar_arrive(bars + 8 * kBarStats);
+  }
+}
+
+// One block of the fold for one query row (thread): O = O * alpha + float(T) * beta, with T read from tensor
+// memory at t_src (this thread's lane) and the factors taken from the block's and the output's references.
+template <int D>
+__device__ __forceinline__ void fold_block(uint32_t t_src, float (&o)[D], float& r_out, float r_blk) {
+  const float r_new = fmaxf(r_out, r_blk);
+  // exact powers of two (the references are integers), and at most one of them differs from 1;
+  // an O that holds nothing yet is multiplied by 0
+  const float alpha = (r_out == r_new) ? 1.0f : pow2_int(fmaxf(r_out - r_new, -127.0f));
+  const float beta = (r_blk == r_new) ? 1.0f : pow2_int(fmaxf(r_blk - r_new, -127.0f));
+  r_out = r_new;
+  const bool plain = !__any_sync(0xffffffffu, alpha != 1.0f || beta != 1.0f);
+  if (plain) {
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t t16[32];
+      ptx::tmem_ld32<0>(t_src + c0, t16);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::add_f32_f16lo(o[c0 + i], t16[i]);
+    }
+  } else {
+    const uint32_t beta16 = __half_as_ushort(__float2half_rn(beta));     // exact, or 0 below 2^-24
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t t16[32];
+      ptx::tmem_ld32<0>(t_src + c0, t16);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::fma_f32_f16lo(t16[i], beta16, o[c0 + i] * alpha);
+    }
   }
 }
 
@@ -293,33 +339,7 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
     if (!ok) break;
     ptx::tc_fence_after();
     const float r_blk = ref_ring[(j % kRefRing) * kTileQ + row];
-    const float r_new = fmaxf(r_out, r_blk);
-    // exact powers of two (the references are integers), and at most one of them differs from 1;
-    // an O that holds nothing yet is multiplied by 0
-    const float alpha = (r_out == r_new) ? 1.0f : pow2_int(fmaxf(r_out - r_new, -127.0f));
-    const float beta = (r_blk == r_new) ? 1.0f : pow2_int(fmaxf(r_blk - r_new, -127.0f));
-    r_out = r_new;
-    const bool plain = !__any_sync(0xffffffffu, alpha != 1.0f || beta != 1.0f);
-    if (plain) {
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t t16[32];
-        ptx::tmem_ld32<0>(t_src + c0, t16);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::add_f32_f16lo(o[c0 + i], t16[i]);
-      }
-    } else {
-      const uint32_t beta16 = __half_as_ushort(__float2half_rn(beta));     // exact, or 0 below 2^-24
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t t16[32];
-        ptx::tmem_ld32<0>(t_src + c0, t16);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = ptx::fma_f32_f16lo(t16[i], beta16, o[c0 + i] * alpha);
-      }
-    }
+    fold_block<D>(t_src, o, r_out, r_blk);
     ptx::tc_fence_before();
     ptx::mbar_arrive(bars + 8 * kBarTFree);
   }

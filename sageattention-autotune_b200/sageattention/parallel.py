@@ -38,6 +38,23 @@ def slice_heads(t: torch.Tensor, tensor_layout: str, lo: int, hi: int) -> torch.
     return t[:, lo:hi] if tensor_layout == "HND" else t[:, :, lo:hi]
 
 
+_gather_groups = {}
+
+
+def _gather_group(group):
+    """The process group the overlapped all-gather runs on.  The attention kernel fills every SM (one CTA
+    per SM, all registers), so a collective issued on an ordinary stream only gets SMs when the kernel it
+    is meant to overlap with has almost finished.  NCCL kernels of a group created with a high-priority
+    stream are placed as soon as any attention CTA retires.  A caller-supplied group is used as it is."""
+    if group is not None or dist.get_backend() != "nccl":
+        return group
+    key = id(dist.group.WORLD)
+    if key not in _gather_groups:
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        _gather_groups[key] = dist.new_group(backend="nccl", pg_options=opts)
+    return _gather_groups[key]
+
+
 def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout: str = "HND",
                      group: Optional[dist.ProcessGroup] = None, gather: bool = True,
                      attn_fn: Optional[Callable] = None, num_kv_heads: Optional[int] = None,
@@ -71,13 +88,15 @@ def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout:
     groups = max(1, min(gather_groups or 4, per_kv))
     bounds = [(g * per_kv // groups, (g + 1) * per_kv // groups) for g in range(groups)]
     on_gpu = q_local.is_cuda
+    if on_gpu:
+        group = _gather_group(group)
     # the gathered output, head-major: (world, per, *rest) with rest = the other dimensions in order
     rest = tuple(q_local.movedim(h_dim, 0).shape[1:])
     full = torch.empty((world, per) + rest, dtype=q_local.dtype, device=q_local.device)
     lse_rest = (q_local.size(0), q_local.size(3 - h_dim))             # (batch, seq)
     lse_full = torch.empty((world, per) + lse_rest, dtype=torch.float32, device=q_local.device) if want_lse else None
     main = torch.cuda.current_stream(q_local.device) if on_gpu else None
-    side = torch.cuda.Stream(q_local.device) if on_gpu else None
+    side = torch.cuda.Stream(q_local.device, priority=-1) if on_gpu else None      # high priority, see _gather_group
 
     def gather_into(dst, slot, lo, hi):
         """all-gather `slot` ((hi - lo) head slots, head-major, contiguous) into dst[:, lo:hi] of every rank"""

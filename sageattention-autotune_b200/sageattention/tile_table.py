@@ -28,7 +28,7 @@ DEFAULT_QK_CONFIG = QK_CONFIGS[0]
 # groupings the sm_100a attention kernels consume: BLKK = WARPK = 64 or 32, i.e. all four
 SUPPORTED_QK_CONFIGS = tuple(c for c in QK_CONFIGS if c[1] == c[3] and c[1] in (32, 64))
 
-KERNEL_NAMES = {0: "two_tile", 1: "one_tile_fold", 2: "two_tile_coupled"}
+KERNEL_NAMES = {0: "two_tile", 1: "one_tile_fold", 2: "two_tile_coupled", 3: "one_tile_persistent"}
 _PV = {"fp32": C.PV_F32, "fp16": C.PV_F16, "fp16+fp32": C.PV_F16_F32, "fp8": C.PV_F8}
 
 

@@ -45,8 +45,11 @@ def _rank(rank, world, port, layout, hq, hkv, groups, queue):
                                     gather_groups=groups, return_lse=True, **kw)
         torch.cuda.synchronize()
         exp, exp_lse = sageattention.sageattn(q, k, v, return_lse=True, **kw)
-        ok = out.shape == q.shape and torch.equal(out, exp) and torch.equal(lse, exp_lse)
-        queue.put((rank, bool(ok)))
+        # (the LSE carries the q.km^T correction, a cuBLAS product whose summation order may follow the batch
+        # of heads it is called with: equal to rounding, not to the bit)
+        same_out = out.shape == q.shape and torch.equal(out, exp)
+        lse_err = float((lse - exp_lse).abs().max())
+        queue.put((rank, bool(same_out and lse_err <= 1e-4), f"output equal: {same_out}, LSE max diff: {lse_err:.3g}"))
     finally:
         dist.destroy_process_group()
 
@@ -66,4 +69,5 @@ def test_sharded_call_gathers_the_single_gpu_result_over_nccl(layout, hq, hkv, g
     for p in procs:
         p.join(300)
         assert p.exitcode == 0
-    assert sorted(queue.get(timeout=5) for _ in range(2)) == [(0, True), (1, True)]
+    results = sorted(queue.get(timeout=5) for _ in range(2))
+    assert [r[:2] for r in results] == [(0, True), (1, True)], results
