@@ -13,8 +13,13 @@
 //     block and publish it after its last;
 //   * the fold warpgroup normalises and stores tile i while the others already work on tile i + 1.
 // Set-up happens once, and a tile's epilogue hides behind the next tile's first blocks.
-// Tiles are dealt to the CTAs round-robin, heaviest (causal) first, which balances a causal launch to
-// about one percent without any global atomic.  Per-tile hand-overs (row sums, references, 1/sum) go
+// Tiles are dealt to the CTAs round-robin over all heads, heaviest (causal) first, which balances a causal
+// launch to about one percent without any global atomic.  The price is locality: CTAs that run together
+// work on different heads, so once the K/V of all heads no longer fit L2 (N = 8192 and up for 64 heads)
+// the kernel turns HBM-bound and the one-CTA-per-tile form wins; the tile table selects this form up to
+// N = 4096.  (Handing tiles out from a global counter in head-major order restores the locality and was
+// measured too: at N >= 16384 it is 1-2 % slower than one CTA per tile, the saved set-up being 3 % of a
+// CTA's life there and the extra hand-over not free; at N = 1024 it is slower than the static deal.)  Per-tile hand-overs (row sums, references, 1/sum) go
 // through eight-slot rings: the softmax can be at most four blocks ahead of the fold, every tile has at
 // least one block, so a slot is never rewritten before it has been read.  At the end of a tile neither
 // softmax warpgroup waits for the other: each thread publishes its row's reference and sum and bumps a

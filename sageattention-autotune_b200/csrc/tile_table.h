@@ -10,8 +10,9 @@
 //     sm_100a kernels consume 128 x 128 score tiles whatever the grouping, so the grouping does not
 //     change their speed, and this one keeps results comparable with the reference's default;
 //   * the kernel: the two-tile kernel (attn_v1.cuh), the one-tile kernel with a fold warpgroup
-//     (attn_v4.cuh, the two-level "fp16+fp32" accumulation only), or the two-tile kernel folding
-//     inside its softmax warps ("coupled": head_dim 256 and 32-key scale blocks in that mode);
+//     (attn_v4.cuh, the two-level "fp16+fp32" accumulation only) as one CTA per query tile or in its
+//     persistent form (attn_v5.cuh), or the two-tile kernel folding inside its softmax warps
+//     ("coupled": head_dim 256 and 32-key scale blocks in that mode);
 //   * how many 128-row query tiles one CTA takes: 1 for the one-tile kernel and for head_dim 256, else 2.
 //     (One tile per CTA on the two-tile kernel was measured as a candidate for short sequences and
 //     lost everywhere, so no entry selects it.)
@@ -41,7 +42,14 @@ inline sage_b200_tile_entry tile_lookup(int head_dim, int is_causal, int pv_accu
     // one-tile kernel against the coupled two-tile kernel, kernel time in ms on B200:
     //   D 128 causal  H 64:  N 1024  0.048 / 0.063    N 4096  0.349 / 0.507    N 32768  16.2 / 24.3
     //   D  64 full    B 16 H 10 N 4096:  1.29 / 1.49
-    e.kernel = SAGE_B200_KERNEL_ONE_TILE_FOLD;
+    // and its persistent form (one CTA per SM walking over the tiles) against one CTA per tile:
+    //   D 128 causal  H 64:  N 1024  0.042 / 0.048    N 4096  0.339 / 0.353    N 16384  4.68 / 4.04    N 32768  20.8 / 16.2
+    //   D  64 full    B 16 H 10 N 4096:  1.20 / 1.29
+    // The persistent form hides a tile's set-up and epilogue, which is what short sequences consist of;
+    // it deals tiles round-robin across all heads, so from N = 8192 on the CTAs running together no
+    // longer share K/V in L2 and the one-CTA-per-tile form (tiles of one head launched next to each
+    // other) wins.
+    e.kernel = (bucket <= 2) ? SAGE_B200_KERNEL_ONE_TILE_PERSISTENT : SAGE_B200_KERNEL_ONE_TILE_FOLD;
     e.q_tiles_per_cta = 1;
   } else {
     e.kernel = (pv_accum == SAGE_B200_PV_F16_F32) ? SAGE_B200_KERNEL_TWO_TILE_COUPLED : SAGE_B200_KERNEL_TWO_TILE;

@@ -206,9 +206,12 @@ def test_tile_table_is_total_and_consistent():
     # the table selects among kernels: the two-level mode runs the one-tile kernel with a fold warpgroup,
     # except at head_dim 256 where only the two-tile kernel has room; the other modes run the two-tile kernel
     assert select_entry(128, True, "fp16+fp32", 32768)["kernel"] == "one_tile_fold"
-    assert select_entry(64, False, "fp16+fp32", 4096)["kernel"] == "one_tile_fold"
+    assert select_entry(128, True, "fp16+fp32", 8192)["kernel"] == "one_tile_fold"
+    # ... in its persistent form (one CTA per SM walking over the tiles) up to 4096 keys
+    assert select_entry(64, False, "fp16+fp32", 4096)["kernel"] == "one_tile_persistent"
+    assert select_entry(128, True, "fp16+fp32", 1024)["kernel"] == "one_tile_persistent"
     assert select_entry(256, True, "fp16+fp32", 4096) == {"qk_config": (128, 64, 32, 64), "kernel": "two_tile_coupled",
                                                            "q_tiles_per_cta": 1, "seq_bucket": 2}
     assert select_entry(128, True, "fp32", 32768)["kernel"] == "two_tile"
     assert select_entry(128, True, "fp32", 32768)["q_tiles_per_cta"] == 2
-    assert len(seen) >= 3
+    assert len(seen) >= 4
