@@ -9,6 +9,7 @@ all-gather of the output (and LSE) when the caller asks for the whole tensor on 
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -85,7 +86,7 @@ def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout:
     rep = num_q_heads // num_kv_heads
     per_kv = -(-num_kv_heads // world)                    # kv-head slots per rank (the last ranks may fill fewer)
     per = per_kv * rep                                    # q-head slots per rank
-    groups = max(1, min(gather_groups or 4, per_kv))
+    groups = max(1, min(gather_groups or int(os.environ.get("SAGE_B200_GATHER_GROUPS", "4")), per_kv))
     bounds = [(g * per_kv // groups, (g + 1) * per_kv // groups) for g in range(groups)]
     on_gpu = q_local.is_cuda
     if on_gpu:
