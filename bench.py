@@ -14,8 +14,8 @@ host<->device copies inside the timed region; `roofline` describes the attention
 with CUDA events inside the same steps); `cpu_baseline` is the CPU restatement of the algorithm
 timed on a bounded sample; `ref_gpu` times the reference's own GPU kernels (its sm80 attention
 kernel compiled for sm_100 and its Triton quantisers as cubins, oracle/_ref) on the same inputs
-after the timed region; with more than one rank a second timed loop adds the NCCL all-gather of
-the output (`gather_ms_per_step`, `value_with_gather`).
+after the timed region; with more than one rank a second timed loop adds the exchange of the output,
+every rank ending with all heads (`gather_ms_per_step`, `value_with_gather`, `gather_via`).
 
 --impl reference times the reference itself, unmodified: when its kernels are present under
 oracle/_ref and a GPU is there, its Triton quantisers + sm80 attention kernel with the fixed
@@ -375,7 +375,10 @@ def main():
     ap.add_argument("--workload", default="c5_32k", choices=sorted(WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--no-gather", action="store_true", help="skip the second timed loop with the NCCL all-gather")
+    ap.add_argument("--no-gather", action="store_true", help="skip the second timed loop with the exchange of the output")
+    ap.add_argument("--gather-via", choices=("peer", "nccl"), default="peer",
+                    help="exchange of the output in the second timed loop: stores into the peers' buffers from the "
+                         "attention epilogue, or the grouped NCCL all-gather")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels after the run")
     ap.add_argument("--attn-only", action="store_true",
                     help="time the attention kernel alone on pre-quantised inputs (tile-table sweeps) and print one line")
@@ -489,14 +492,17 @@ def main():
                          "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": (qbytes / (front_ms * 1e-3) / 1e9) / pk["hbm_gbs"] if front_ms else None}
 
-    # ---- the same step with the output all-gathered over NCCL (every rank ends with all heads), overlapped
-    # with the compute per head group by sageattn_sharded
-    gather_ms = None
+    # ---- the same step with the output exchanged (every rank ends with all heads): rows stored into every
+    # rank's buffer by the attention epilogue, or NCCL all-gathers overlapped per head group (sageattn_sharded)
+    gather_ms = plain_again_ms = None
     if world > 1 and not args.no_gather:
         def step_gather():
             out_holder["g"] = sageattn_sharded(q, k, v, num_q_heads=w["Hq"], num_kv_heads=w["Hkv"], gather=True,
-                                               attn_fn=attn_call, **kw)
+                                               attn_fn=attn_call, gather_via=args.gather_via, **kw)
         gather_ms = timed(step_gather, args.steps, 2) / args.steps
+        # the plain step once more, right after: the two loops run minutes apart under a power cap, and the
+        # difference between them is only meaningful next to the drift of the plain step itself
+        plain_again_ms = timed(step, args.steps, 1) / args.steps
 
     # ---- end to end from pinned host memory
     e2e = None
@@ -528,7 +534,9 @@ def main():
                 "gpu_launches": int(launches) * world,
                 "gpu_launches_note": "kernels of libsage_b200.so launched inside the timed region, counted by the library "
                                      "(sage_b200_launch_count) on rank 0, times the number of ranks",
-                "gather_ms_per_step": gather_ms,
+                "gather_ms_per_step": gather_ms, "ms_per_step_after_gather_loop": plain_again_ms,
+                "gather_overhead_ms": (gather_ms - 0.5 * (ms_per_step + plain_again_ms)) if gather_ms else None,
+                "gather_via": args.gather_via if gather_ms else None,
                 "value_with_gather": (F_lit / (gather_ms * 1e-3) / 1e12) if gather_ms else None}
         if not args.no_ref_gpu and world == 1 and reference_gpu_available(w):
             # the reference's own GPU kernels on the same inputs, after (never inside) the timed region

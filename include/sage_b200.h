@@ -284,6 +284,28 @@ int sage_b200_attn_fwd_fp8(const int8_t* q, const int8_t* k, const void* v, cons
                            float sm_scale, int blk_q, int blk_k, int warp_q, int warp_k, int granularity,
                            void* stream);
 
+/*
+ * Head sharding over the GPUs of one node, one process per GPU, with the exchange of the output fused
+ * into the attention epilogue.  The reference is single-GPU (its launcher writes one output tensor,
+ * csrc/qattn/qk_int8_sv_f16_launch_sm80.cuh:138-209); these entry points have no counterpart there.
+ *
+ * Every process allocates one buffer for the WHOLE output with sage_b200_peer_alloc, sends the 64-byte
+ * handle to the other processes (any host channel) and maps theirs with sage_b200_peer_open.  A thread
+ * then names the other ranks' buffers with sage_b200_set_output_peers: byte_offsets[i] = (peer i's
+ * mapped base) - (own base).  From then on every attention launch of that thread whose `out` lies in
+ * the own buffer stores each finished row to out + byte_offsets[i] as well, with plain 32-byte stores
+ * over NVLink, until the set is cleared with n = 0.  The stores of a launch have been performed when
+ * the launch has completed; the ranks still have to meet (a barrier or any collective on the same
+ * streams) before one reads what another wrote.  With peers set, `out` must be 32-byte aligned and its
+ * strides multiples of 16 elements.  n <= 7.  Rows a CTA gives up on read as NaN in every copy.
+ */
+#define SAGE_B200_PEER_HANDLE_BYTES 64
+int sage_b200_peer_alloc(size_t bytes, void** ptr, unsigned char* handle /* [64] out */);
+int sage_b200_peer_open(const unsigned char* handle /* [64] */, void** ptr);
+int sage_b200_peer_close(void* ptr);   /* a pointer from sage_b200_peer_open */
+int sage_b200_peer_free(void* ptr);    /* a pointer from sage_b200_peer_alloc, after every peer closed it */
+int sage_b200_set_output_peers(int n, const int64_t* byte_offsets);
+
 #ifdef __cplusplus
 }
 #endif

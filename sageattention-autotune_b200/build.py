@@ -26,7 +26,7 @@ TORCH_LIB = os.path.join(HERE, "sageattention", "libsage_b200_torch.so")
 # (libstdc++.so) with torch, and a relocated toolchain that only ships libstdc++.a links a private
 # copy in, after which an exception thrown by an operator kills the process instead of reaching Python.
 CXX = os.environ.get("SAGE_B200_CXX", "g++")
-SOURCES = ["api.cu", "quant.cu", "attn_fwd.cu"]
+SOURCES = ["api.cu", "quant.cu", "attn_fwd.cu", "peer.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-DSAGE_B200_BUILD"]

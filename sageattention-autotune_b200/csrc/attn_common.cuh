@@ -20,6 +20,8 @@ constexpr float kMagicF = 12582912.0f;            // 1.5 * 2^23
 constexpr uint32_t kMagicI = 0x4B400000u;
 constexpr float kLazyRescale = 8.0f;              // fp32 accumulators: rescale O only if max grew by 2^8
 
+constexpr int kMaxPeers = kMaxOutputPeers;      // a node has at most eight GPUs
+
 struct AttnParams {
   const float* q_scale;
   const float* k_scale;
@@ -37,7 +39,25 @@ struct AttnParams {
   int64_t os_b, os_h, os_n;
   unsigned long long launch_id;  // non-zero, unique per launch of this process (see g_attn_abort)
   long long wait_cycles;         // budget of every bounded wait, in SM clocks
+  // Copies of the output in other GPUs' memory (head sharding with the exchange fused into the epilogue):
+  // every row of the output is also stored at the same address plus peer_off[i], i < n_peer.  No fence
+  // follows the stores: they are only read after the launch has completed (a system-scope fence per CTA
+  // was measured and cost 6 % of a step for nothing).
+  int n_peer;
+  long long peer_off[kMaxPeers];
 };
+
+// The same 32 bytes (16 output values) to every peer copy of the output: plain stores that travel over
+// NVLink, 32 bytes per store so that each request carries one whole sector.  `dst` is the address in the
+// local output.
+__device__ __forceinline__ void store_peers32(const AttnParams& p, const unsigned short* dst, const uint32_t* w) {
+  for (int i = 0; i < p.n_peer; ++i) {
+    const char* d = reinterpret_cast<const char*>(dst) + p.peer_off[i];
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(d), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+  }
+}
 
 // Abort protocol.  When a bounded wait runs out, the CTA records {launch id, wall time} in a device
 // word pair; CTAs of the same launch that start later see it and return at once, so a launch whose
@@ -83,8 +103,10 @@ __device__ __forceinline__ void poison_rows(const AttnParams& p, int rows, int q
     const int r = q0 + i / (head_dim / 8);
     if (r < p.len_q) {
       unsigned short* orow = static_cast<unsigned short*>(p.out) + b * p.os_b + h * p.os_h + r * p.os_n;
-      *reinterpret_cast<uint4*>(orow + (i % (head_dim / 8)) * 8) =
-          make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu);
+      const uint4 nan8 = make_uint4(0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu, 0x7fff7fffu);
+      unsigned short* at = orow + (i % (head_dim / 8)) * 8;
+      *reinterpret_cast<uint4*>(at) = nan8;
+      for (int j = 0; j < p.n_peer; ++j) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(at) + p.peer_off[j]) = nan8;
     }
   }
 }

@@ -237,6 +237,12 @@ static int attn_fwd_impl(const int8_t* q, const int8_t* k, const void* v, const 
   p.os_h = o_strides[1];
   p.os_n = o_strides[2];
   p.wait_cycles = g_wait_cycles.load(std::memory_order_relaxed);
+  const PeerSet& peers = output_peers();
+  p.n_peer = peers.n;
+  for (int i = 0; i < kMaxPeers; ++i) p.peer_off[i] = i < peers.n ? peers.off[i] : 0;
+  SAGE_REQUIRE(peers.n == 0 || ((reinterpret_cast<uintptr_t>(out) & 31u) == 0 && o_strides[0] % 16 == 0 &&
+                                o_strides[1] % 16 == 0 && o_strides[2] % 16 == 0),
+               "attn_fwd: with output peers the output must be 32-byte aligned with strides % 16 == 0");
 
   constexpr int kStageRows = 128;   // keys per TMA stage in both kernels
   CUtensorMap mq, mk, mv;

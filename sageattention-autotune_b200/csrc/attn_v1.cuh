@@ -422,6 +422,8 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 #pragma unroll
           for (int i = 0; i < 16; i += 4)
             *reinterpret_cast<uint4*>(orow + c0 + 2 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+          store_peers32(p, orow + c0, w);
+          store_peers32(p, orow + c0 + 16, w + 8);
         }
       }
     } else {
@@ -449,6 +451,8 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, uint32_t bars,
 #pragma unroll
           for (int i = 0; i < 16; i += 4)
             *reinterpret_cast<uint4*>(orow + c0 + 2 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+          store_peers32(p, orow + c0, w);
+          store_peers32(p, orow + c0 + 16, w + 8);
         }
       }
     }

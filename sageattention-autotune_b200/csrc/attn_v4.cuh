@@ -82,6 +82,26 @@ struct SmemPlan {
   static constexpr int kDynamic = kTotal + 1024;             // slack for manual 1024-byte alignment
 };
 
+// One normalised output row (this thread's, fp32 in registers) to every peer copy of the output, peer by
+// peer so that one address is live at a time.
+template <int D, int OUT_DTYPE>
+__device__ __forceinline__ void store_row_peers(const AttnParams& p, const unsigned short* orow, const float (&o)[D],
+                                                float inv) {
+#pragma unroll 1
+  for (int i = 0; i < p.n_peer; ++i) {
+    const char* d = reinterpret_cast<const char*>(orow) + p.peer_off[i];
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 16) {
+      uint32_t w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w[k] = pack_out<OUT_DTYPE>(o[c0 + 2 * k] * inv, o[c0 + 2 * k + 1] * inv);
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(d + 2 * c0), "r"(w[0]), "r"(w[1]),
+                   "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                   : "memory");
+    }
+  }
+}
+
 __device__ __forceinline__ int k_class(int c) { return ((c >> 6) << 2) | ((c & 7) >> 1); }
 
 // 2^k for an integer-valued k <= 0, exactly; 0 below the normal range
@@ -325,7 +345,7 @@ __device__ __forceinline__ void fold_block(uint32_t t_src, float (&o)[D], float&
 template <int D, int OUT_DTYPE>
 __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, uint32_t tmem_base,
                                           volatile int* abort_flag, const float* ref_ring, const float* inv_in,
-                                          int row, int n_blocks, int q_row0, int b, int h) {
+                                          uint8_t* stage, int row, int n_blocks, int q_row0, int b, int h) {
   const uint32_t lane_base = static_cast<uint32_t>(row & ~31) << 16;
   const uint32_t t_src = tmem_base + lane_base + 384;
   float o[D];                  // this row of the fp32 output, relative to 2^r_out
@@ -355,6 +375,39 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
 #pragma unroll
         for (int i = 0; i < 4; ++i) w[i] = pack_out<OUT_DTYPE>(o[c0 + 2 * i] * inv, o[c0 + 2 * i + 1] * inv);
         *reinterpret_cast<uint4*>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    if (p.n_peer > 0) {
+      // The same rows to every peer copy of the output.  A row per thread would leave the SM as 32-byte
+      // requests, and a CTA does not retire before its requests over NVLink have been answered, so the
+      // warp first lays its 32 rows out in shared memory (the first V stage: every block has been folded,
+      // neither TMA nor the tensor core touches the stages any more) and then stores them with consecutive
+      // lanes on consecutive 16-byte pieces: whole rows per request.
+      constexpr int kPieces = D / 8;                       // 16-byte pieces of a row
+      constexpr int kRowsPerStore = 32 / kPieces;
+      uint8_t* mine = stage + (row & ~31) * (D * 2);       // this warp's rows
+      const int lane = row & 31;
+#pragma unroll
+      for (int c = 0; c < kPieces; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = pack_out<OUT_DTYPE>(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
+        *reinterpret_cast<uint4*>(mine + lane * (D * 2) + ((c ^ (lane % kPieces)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      __syncwarp();
+      const int c = lane % kPieces;
+      char* tile_out = reinterpret_cast<char*>(static_cast<unsigned short*>(p.out) + b * p.os_b + h * p.os_h) + c * 16;
+#pragma unroll 1
+      for (int i = 0; i < p.n_peer; ++i) {
+        char* dst = tile_out + p.peer_off[i];
+#pragma unroll 4
+        for (int r0 = 0; r0 < 32; r0 += kRowsPerStore) {
+          const int r = r0 + lane / kPieces;
+          const int gq = q_row0 + (row & ~31) + r;
+          if (gq < p.len_q)
+            *reinterpret_cast<uint4*>(dst + gq * p.os_n * 2) =
+                *reinterpret_cast<const uint4*>(mine + r * (D * 2) + ((c ^ (r % kPieces)) << 4));
+        }
       }
     }
   }
@@ -436,7 +489,7 @@ sage_attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     threadIdx.x & 127, n_blk, q0, b, h);
   } else if (warp < 12) {
     ptx::reg_inc<kRegsFold>();
-    fold_role<D, OUT_DTYPE>(p, bars, tmem_base, abort_flag, ref_ring, inv_buf, threadIdx.x - 256, n_blk, q0, b, h);
+    fold_role<D, OUT_DTYPE>(p, bars, tmem_base, abort_flag, ref_ring, inv_buf, smem_gen + Plan::kVOff, threadIdx.x - 256, n_blk, q0, b, h);
   } else {
     ptx::reg_dec<kRegsIssue>();
     if (warp == 12 && lane == 0) {

@@ -236,6 +236,7 @@ __device__ __forceinline__ void fold_role(const AttnParams& p, uint32_t bars, ui
         for (int i = 0; i < 4; ++i) wd[i] = pack_out<OUT_DTYPE>(o[c0 + 2 * i] * inv, o[c0 + 2 * i + 1] * inv);
         *reinterpret_cast<uint4*>(orow + c0) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
       }
+      if (p.n_peer > 0) v4::store_row_peers<D, OUT_DTYPE>(p, orow, o, inv);
     }
     w.next(p);
   }

@@ -31,6 +31,15 @@ void count_launch();
     if (!(cond)) return ::sage::fail(SAGE_B200_ERR_INVALID, __VA_ARGS__); \
   } while (0)
 
+// Copies of the attention output in other GPUs' memory, for the launches of the calling thread
+// (sage_b200_set_output_peers): byte offsets from the local output to each copy.
+constexpr int kMaxOutputPeers = 7;
+struct PeerSet {
+  int n = 0;
+  long long off[kMaxOutputPeers] = {};
+};
+PeerSet& output_peers();
+
 // Programmatic dependent launch.  Inside one sage_b200_sageattn call the kernels form a chain on one
 // stream; every kernel after the first is launched with the programmatic-serialisation attribute, so its
 // CTAs may be placed (and run their set-up) while the previous kernel drains.  Each kernel of the

@@ -27,6 +27,8 @@ EXPORTS = (
     "sage_b200_cast_v_f16", "sage_b200_attn_fwd", "sage_b200_quant_v_fp8_scratch_bytes", "sage_b200_quant_v_fp8",
     "sage_b200_attn_fwd_fp8", "sage_b200_smooth_v_f16", "sage_b200_attn_fwd_fuse_v_mean",
     "sage_b200_sageattn_workspace_bytes", "sage_b200_sageattn", "sage_b200_set_wait_budget", "sage_b200_launch_count", "sage_b200_tile_lookup",
+    "sage_b200_peer_alloc", "sage_b200_peer_open", "sage_b200_peer_close", "sage_b200_peer_free",
+    "sage_b200_set_output_peers",
 )
 
 _lib = None
@@ -95,6 +97,16 @@ def lib() -> ctypes.CDLL:
         L.sage_b200_launch_count.restype = ctypes.c_ulonglong
         L.sage_b200_set_wait_budget.restype = ctypes.c_longlong
         L.sage_b200_set_wait_budget.argtypes = [ctypes.c_longlong]
+        L.sage_b200_peer_alloc.restype = i
+        L.sage_b200_peer_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
+        L.sage_b200_peer_open.restype = i
+        L.sage_b200_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        L.sage_b200_peer_close.restype = i
+        L.sage_b200_peer_close.argtypes = [vp]
+        L.sage_b200_peer_free.restype = i
+        L.sage_b200_peer_free.argtypes = [vp]
+        L.sage_b200_set_output_peers.restype = i
+        L.sage_b200_set_output_peers.argtypes = [i, i64p]
         _lib = L
     return _lib
 

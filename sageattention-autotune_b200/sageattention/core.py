@@ -31,6 +31,37 @@ _PV_CODE = {"fp32": C.PV_F32, "fp16": C.PV_F16, "fp16+fp32": C.PV_F16_F32}
 _FP8_PV = "fp8"      # internal selector of the e4m3 P.V kernel
 
 
+import contextlib
+import threading
+
+_into = threading.local()
+
+
+@contextlib.contextmanager
+def output_into(buffer: torch.Tensor):
+    """Inside the block, the attention calls of this thread write their output into `buffer` (same
+    shape and dtype as q, head_dim a supported size so that nothing is padded) instead of a fresh
+    tensor, and return it.  Used by the head-sharded call, whose output lives in memory that the
+    other GPUs of the node have mapped."""
+    previous = getattr(_into, "buffer", None)
+    _into.buffer = buffer
+    try:
+        yield
+    finally:
+        _into.buffer = previous
+
+
+def _new_output(q: torch.Tensor, head_dim: int) -> torch.Tensor:
+    buffer = getattr(_into, "buffer", None)
+    if buffer is None:
+        return torch.empty(q.size(), dtype=q.dtype, device=q.device)
+    if buffer.shape != q.shape or buffer.dtype != q.dtype or buffer.device != q.device or head_dim != q.size(-1):
+        raise ValueError("output_into: the buffer must have q's shape (an unpadded head_dim), dtype and device")
+    if buffer.stride(-1) != 1:
+        raise ValueError("output_into: the last dimension of the buffer must be contiguous")
+    return buffer
+
+
 # When set to a list, (label, start_event, end_event) is appended around each group of kernel
 # launches, so that callers (the benchmark) can time the attention kernel alone inside a full call.
 _profile = None
@@ -201,7 +232,7 @@ def _sageattn_one_call(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smooth
     nbytes = L.sage_b200_sageattn_workspace_bytes(dt, b, hq, hkv, nq, nk, d, blk_q, blk_k, warp_q, warp_k, gran,
                                                   1 if smooth_k else 0, cast_v)
     work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-    output = torch.empty(q.size(), dtype=q.dtype, device=dev)
+    output = _new_output(q, head_dim)
     lse = torch.empty((b, hq, nq), dtype=torch.float32, device=dev) if return_lse else None
     km = None
     if return_lse and smooth_k:
@@ -343,7 +374,7 @@ def _sageattn_configured(q, k, v, tensor_layout, is_causal, pv_accum_dtype, smoo
         else:
             v_fp16 = cast_v_fp16(v, tensor_layout)
 
-    output = torch.empty(q.size(), dtype=dtype, device=q.device)
+    output = _new_output(q, head_dim)
     with _Timed("attn"):
         lse = attn_fwd_quantized(q_int8, k_int8, v_fp16, output, q_scale, k_scale, tensor_layout, is_causal,
                                  sm_scale, qk_config, pv_accum_dtype, return_lse, qk_quant_gran, v_scale, v_mean)

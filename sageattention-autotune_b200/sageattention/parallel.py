@@ -6,10 +6,18 @@ multi-GPU form is one process per GPU, each running the unchanged single-GPU pip
 contiguous range of kv-heads together with the query heads that share them (GQA groups are never
 split).  No kernel touches another GPU's memory.  NCCL is used for exactly one thing: an
 all-gather of the output (and LSE) when the caller asks for the whole tensor on every rank.
+
+On the GPUs of one node the default exchange is not a collective at all: every rank keeps the whole output
+in a buffer that the other ranks have mapped (sage_b200_peer_alloc / sage_b200_peer_open), and the attention
+epilogue stores each finished row into every rank's buffer (sage_b200_set_output_peers), so the transfer
+over NVLink runs tile by tile under the compute and only a small collective that makes the ranks meet
+follows the kernel.
 """
 from __future__ import annotations
 
+import ctypes
 import os
+import warnings
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -56,10 +64,152 @@ def _gather_group(group):
     return _gather_groups[key]
 
 
+class _RawCuda:
+    """A device allocation seen through the CUDA array interface, for torch.as_tensor."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerOutput:
+    """The whole output on every rank, each rank's copy mapped by all the others.
+
+    Two buffers are used in turn: the tensor a call returns stays valid until the call after the next
+    one with the same shapes, and a rank that is already storing the next call's rows into its peers'
+    memory never touches what they may still be reading."""
+
+    def __init__(self, shape, dtype, device, group):
+        from . import _capi as C
+        self._C = C
+        L = C.lib()
+        self.shape, self.dtype, self.device = tuple(shape), dtype, device
+        self.nbytes = -(-(torch.empty((), dtype=dtype).element_size() * int(torch.Size(shape).numel())) // 256) * 256
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.bases, self.opened, self.tensors, self.offsets = [], [], [], []
+        self.ok = True
+        self.turn = 0
+        for _ in range(2):
+            ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            with torch.cuda.device(device):
+                rc = L.sage_b200_peer_alloc(self.nbytes, ctypes.byref(ptr), handle)
+            mine = bytes(handle.raw) if rc == 0 else None
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+            peers = []
+            if all(h is not None for h in handles):
+                with torch.cuda.device(device):
+                    for r in range(world):
+                        if r == rank:
+                            continue
+                        mapped = ctypes.c_void_p()
+                        if L.sage_b200_peer_open(handles[r], ctypes.byref(mapped)) != 0:
+                            self.ok = False
+                            break
+                        peers.append(mapped.value)
+                        self.opened.append(mapped.value)
+            else:
+                self.ok = False
+            if rc == 0:
+                self.bases.append(ptr.value)
+            flags = [None] * world
+            dist.all_gather_object(flags, self.ok, group=group)
+            self.ok = all(flags)
+            if not self.ok:
+                self.reason = L.sage_b200_last_error().decode()
+                break
+            raw = torch.as_tensor(_RawCuda(ptr.value, self.nbytes), device=device)
+            n = int(torch.Size(shape).numel())
+            self.tensors.append(raw.view(dtype)[:n].view(self.shape))
+            self.offsets.append((ctypes.c_int64 * max(1, len(peers)))(*[b - ptr.value for b in peers]))
+        self.n_peer = world - 1
+
+    def next(self):
+        """(tensor, offsets) of the buffer this call writes"""
+        self.turn ^= 1
+        return self.tensors[self.turn], self.offsets[self.turn]
+
+    def close(self):
+        """Unmap the peers' buffers and free the own ones (every rank, after a barrier of the caller's)."""
+        L = self._C.lib()
+        with torch.cuda.device(self.device):
+            for p in self.opened:
+                L.sage_b200_peer_close(p)
+            for p in self.bases:
+                L.sage_b200_peer_free(p)
+        self.opened, self.bases, self.tensors = [], [], []
+
+
+_peer_outputs = {}
+
+
+def _peer_output(shape, dtype, device, group) -> Optional[PeerOutput]:
+    key = (tuple(shape), dtype, device, id(group))
+    if key not in _peer_outputs:
+        ws = PeerOutput(shape, dtype, device, group)
+        if not ws.ok:
+            warnings.warn(f"peer-mapped output buffers are not available ({ws.reason}); the output is gathered by NCCL",
+                          stacklevel=3)
+        _peer_outputs[key] = ws
+    ws = _peer_outputs[key]
+    return ws if ws.ok else None
+
+
+def release_peer_outputs() -> None:
+    """Free every peer-mapped output buffer of this process (collective: all ranks call it together,
+    with no attention call in flight)."""
+    if dist.is_initialized():
+        dist.barrier()
+    for ws in _peer_outputs.values():
+        ws.close()
+    _peer_outputs.clear()
+
+
+def _sharded_into_peers(q_local, k_local, v_local, num_q_heads, num_kv_heads, tensor_layout, group, attn_fn, kwargs):
+    """The head-sharded call with the exchange fused into the attention epilogue; None when the peer
+    buffers cannot be had (the caller then gathers by NCCL)."""
+    from . import _capi as C
+    from .core import output_into, sageattn
+    attn_fn = attn_fn or sageattn
+    h_dim = 1 if tensor_layout == "HND" else 2
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    full_shape = list(q_local.shape)
+    full_shape[h_dim] = num_q_heads
+    ws = _peer_output(full_shape, q_local.dtype, q_local.device, group)
+    if ws is None:
+        return None
+    want_lse = bool(kwargs.get("return_lse"))
+    (q_lo, q_hi), _ = local_heads(num_q_heads, num_kv_heads, world, rank)
+    full, offsets = ws.next()
+    L = C.lib()
+    lse = None
+    if q_hi > q_lo:
+        C.check(L.sage_b200_set_output_peers(ws.n_peer, offsets))
+        try:
+            with output_into(slice_heads(full, tensor_layout, q_lo, q_hi)):
+                res = attn_fn(q_local, k_local, v_local, tensor_layout=tensor_layout, **kwargs)
+        finally:
+            L.sage_b200_set_output_peers(0, None)
+        lse = res[1] if want_lse else None
+    # the ranks meet: once this collective has completed here, every rank's attention kernel has, and with it
+    # its stores into this rank's buffer
+    per = -(-num_kv_heads // world) * (num_q_heads // num_kv_heads)
+    if want_lse:
+        b, n = q_local.size(0), q_local.size(3 - h_dim)
+        slot = torch.zeros((per, b, n), dtype=torch.float32, device=q_local.device)
+        if lse is not None:
+            slot[: lse.size(1)] = lse.movedim(1, 0)
+        lse_full = torch.empty((world * per, b, n), dtype=torch.float32, device=q_local.device)
+        dist.all_gather_into_tensor(lse_full, slot, group=group)
+        return full, lse_full[:num_q_heads].movedim(0, 1)
+    meet = torch.zeros(1, dtype=torch.int32, device=q_local.device)
+    dist.all_reduce(meet, group=group)
+    return full
+
+
 def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout: str = "HND",
                      group: Optional[dist.ProcessGroup] = None, gather: bool = True,
                      attn_fn: Optional[Callable] = None, num_kv_heads: Optional[int] = None,
-                     gather_groups: Optional[int] = None, **kwargs):
+                     gather_groups: Optional[int] = None, gather_via: Optional[str] = None, **kwargs):
     """Run attention on this rank's heads; optionally all-gather the full output.
 
     q_local/k_local/v_local hold only this rank's heads (as produced by `local_heads` +
@@ -69,7 +219,24 @@ def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout:
     `num_q_heads` heads in the input layout, and the collective is overlapped with the compute: the
     local kv-heads are processed in `gather_groups` groups (default: up to 4), and while group g+1 is
     computed on the current stream, group g is all-gathered by NCCL on a side stream.  `attn_fn`
-    defaults to sageattention.sageattn."""
+    defaults to sageattention.sageattn.
+
+    `gather_via`: "peer" stores the output rows straight into every rank's copy of the output from the
+    attention epilogue (GPUs of one node, at most eight ranks, an attention function of this package, a head_dim
+    of 64, 128 or 256); the returned tensor then lives in a buffer that is reused by the call after the
+    next one with the same shapes.  "nccl" is the grouped all-gather described above.  The default (also
+    settable as SAGE_B200_GATHER) is "peer" where it applies, else "nccl"."""
+    via = gather_via or os.environ.get("SAGE_B200_GATHER", "peer")
+    if via not in ("peer", "nccl"):
+        raise ValueError("gather_via must be 'peer' or 'nccl'")
+    own_fn = attn_fn is None or getattr(attn_fn, "__module__", "") == __name__.rsplit(".", 1)[0] + ".core"
+    if (via == "peer" and gather and own_fn and q_local.is_cuda and dist.is_initialized()
+            and 1 < dist.get_world_size(group) <= 8 and dist.get_backend(group) == "nccl"
+            and q_local.size(-1) in (64, 128, 256)):
+        kv = num_q_heads if num_kv_heads is None else num_kv_heads
+        res = _sharded_into_peers(q_local, k_local, v_local, num_q_heads, kv, tensor_layout, group, attn_fn, kwargs)
+        if res is not None:
+            return res
     if attn_fn is None:
         from .core import sageattn as attn_fn
     h_dim = 1 if tensor_layout == "HND" else 2

@@ -215,3 +215,15 @@ def test_tile_table_is_total_and_consistent():
     assert select_entry(128, True, "fp32", 32768)["kernel"] == "two_tile"
     assert select_entry(128, True, "fp32", 32768)["q_tiles_per_cta"] == 2
     assert len(seen) >= 4
+
+
+def test_output_peers_arguments_are_checked():
+    import ctypes
+    from sageattention import _capi as C
+    L = C.lib()
+    bad = (ctypes.c_int64 * 8)(*([64] * 8))
+    assert L.sage_b200_set_output_peers(8, bad) != 0 and b"between 0 and 7" in L.sage_b200_last_error()
+    odd = (ctypes.c_int64 * 1)(48)
+    assert L.sage_b200_set_output_peers(1, odd) != 0 and b"multiple of 32" in L.sage_b200_last_error()
+    assert L.sage_b200_set_output_peers(1, None) != 0
+    assert L.sage_b200_set_output_peers(0, None) == 0
