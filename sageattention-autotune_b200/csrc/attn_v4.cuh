@@ -110,17 +110,166 @@ __device__ __forceinline__ float pow2_int(float k) {
   return __int_as_float(e << 23);
 }
 
+// Integer maxima of one 32-column chunk of scores, per scale class (class t owns columns 2t + 8i and
+// 2t + 8i + 1): three-input maxima, started from the chunk (`first`) or continued from `mx`.
+__device__ __forceinline__ void chunk_max(const uint32_t (&s)[32], int (&mx)[4], bool first) {
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    int v[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = static_cast<int>(s[2 * t + 8 * i]);
+      v[2 * i + 1] = static_cast<int>(s[2 * t + 8 * i + 1]);
+    }
+    int m;
+    if (first) {
+      m = __vimax3_s32(v[0], v[1], v[2]);
+      m = __vimax3_s32(m, v[3], v[4]);
+      m = __vimax3_s32(m, v[5], v[6]);
+      m = max(m, v[7]);
+    } else {
+      m = __vimax3_s32(mx[t], v[0], v[1]);
+      m = __vimax3_s32(m, v[2], v[3]);
+      m = __vimax3_s32(m, v[4], v[5]);
+      m = __vimax3_s32(m, v[6], v[7]);
+    }
+    mx[t] = m;
+  }
+}
+
+// Share of 2^x evaluated with a polynomial on the FMA pipe instead of ex2.approx.  Here 0 is best
+// (N = 32768 causal, sustained: 18.1 ms with 0/8, 18.4 with 1/8, 18.9 with 2/8, 19.6 with 3/8): with
+// two warpgroups out of phase the special-function unit is not the limiter and the extra
+// instructions only cost power.  The two-tile kernel (attn_v1.cuh) is issue-bound and keeps 3/8.
+#ifndef SAGE_V4_POLY
+#define SAGE_V4_POLY 0
+#endif
+
+// P = 2^(S*a - ref) for one 32-column chunk: X = float(S) + 1.5*2^23 without a conversion (|S| < 2^22), then
+// p = 2^(X*a + neg) with neg = -(1.5*2^23*a + ref), two columns of one class per packed FMA.  The 32 scores
+// in `s` are replaced by 16 registers of fp16 pairs; the row sums go to the two packed accumulators.
+__device__ __forceinline__ void chunk_exp(uint32_t (&s)[32], const unsigned long long (&a2)[4],
+                                          const unsigned long long (&neg2)[4], unsigned long long& acc0,
+                                          unsigned long long& acc1) {
+  constexpr int kPolyDen = 8, kPolyNum = SAGE_V4_POLY;
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    const unsigned long long e0 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 0] + kMagicI), __uint_as_float(s[c + 1] + kMagicI)),
+                                            a2[(c & 7) >> 1], neg2[(c & 7) >> 1]);
+    const unsigned long long e1 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 2] + kMagicI), __uint_as_float(s[c + 3] + kMagicI)),
+                                            a2[((c + 2) & 7) >> 1], neg2[((c + 2) & 7) >> 1]);
+    float p0, p1, p2, p3;
+    if (((c >> 2) % kPolyDen) < kPolyNum) {
+      ptx::exp2_pair_poly(e0, p0, p1);
+      ptx::exp2_pair_poly(e1, p2, p3);
+    } else {
+      float x0, x1, x2, x3;
+      ptx::unpack2(e0, x0, x1);
+      ptx::unpack2(e1, x2, x3);
+      p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
+    }
+    acc0 = ptx::add2(acc0, ptx::pack2(p0, p1));
+    acc1 = ptx::add2(acc1, ptx::pack2(p2, p3));
+    s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
+    s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
+  }
+}
+
+// The new reference of a warpgroup after a block with maximum m_blk: integer, at least this block's
+// maximum, never below anything already used, and not below the other warpgroup's reference of block
+// j-3.  That block's softmax finished before the scores of block j could be issued, so the value is
+// always the same one: results do not depend on how the two warpgroups happen to interleave.
+// (references move in steps of kRefStep: coarse enough that the two warpgroups nearly always agree
+// and the fold stays a plain add, fine enough that P keeps its fp16 precision: P's largest value in
+// a row is at least 2^-kRefStep)
+__device__ __forceinline__ float next_reference(float ref, float m_blk, float r_other) {
+  return fmaxf(fmaxf(ref, ceilf(m_blk * (1.0f / kRefStep)) * kRefStep), r_other);
+}
+
 // One block of the softmax for one query row (thread): the scores of buffer t_s (this thread's lane) become
 // P in place, `ref` and `d_sum` (this warpgroup's reference exponent and row sum) are brought up to date,
 // and the block's reference is published for the fold warps and the other warpgroup.  `a` are the eight
 // dequantisation constants of the block, `r_other` the other warpgroup's reference of three blocks
 // earlier (or -inf), `lim` the last visible column when `need_mask`.  The caller waits for the scores
 // before and signals P after.
+//
+// The scores stay in tensor memory and are read twice, 32 columns at a time (holding all 128 would cost
+// the registers the fold warps need for O): pass 1 finds the block maximum, pass 2 writes P.  In a block
+// without masked columns the reads are pipelined: the load of the next chunk is in flight while the
+// current one is worked on, so only the very first load of a block is waited for in full.
 __device__ __forceinline__ void softmax_block(uint32_t t_s, const float (&a)[8], bool need_mask, int lim, float r_other,
                                               float& ref, float& d_sum, float* ref_ring_slot,
                                               volatile float* ref_pub_slot) {
-  // pass 1: the block maximum, 64 columns at a time (the scores stay in tensor memory and are read
-  // again in pass 2: holding all 128 would cost the registers the fold warps need for O)
+  if (!need_mask) {
+    uint32_t sa[32], sb[32];
+    int mx[4];
+    // ---- pass 1
+    ptx::tmem_ld32<0>(t_s, sa);
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld32<0>(t_s + 32, sb);
+    chunk_max(sa, mx, true);
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld32<0>(t_s + 64, sa);
+    chunk_max(sb, mx, false);
+    float m_blk = fmaxf(fmaxf(static_cast<float>(mx[0]) * a[0], static_cast<float>(mx[1]) * a[1]),
+                        fmaxf(static_cast<float>(mx[2]) * a[2], static_cast<float>(mx[3]) * a[3]));
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld32<0>(t_s + 96, sb);
+    chunk_max(sa, mx, true);
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld32<0>(t_s, sa);                          // the first chunk again, for pass 2
+    chunk_max(sb, mx, false);
+    m_blk = fmaxf(m_blk, fmaxf(fmaxf(static_cast<float>(mx[0]) * a[4], static_cast<float>(mx[1]) * a[5]),
+                               fmaxf(static_cast<float>(mx[2]) * a[6], static_cast<float>(mx[3]) * a[7])));
+
+    const float r_new = next_reference(ref, m_blk, r_other);
+    // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
+    const float m_ref = (r_new == -INFINITY) ? 0.0f : r_new;
+    const float shrink = (ref == r_new) ? 1.0f : pow2_int(fmaxf(ref - m_ref, -127.0f));
+    ref = r_new;
+    *ref_pub_slot = r_new;
+    *ref_ring_slot = r_new;       // (slot reuse: the block eight before was folded, and read by the other warpgroup, long ago)
+
+    // ---- pass 2: the P of chunk q (32 keys, 16 registers) overwrites score columns [16 q, 16 q + 16), which
+    // pass 2 has consumed by then; the load in flight at that moment reads columns further up
+    unsigned long long a2[4], neg2[4];
+    unsigned long long acc0 = ptx::pack2(0.0f, 0.0f), acc1 = acc0;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float ng = fmaf(-kMagicF, a[t], -m_ref);
+      a2[t] = ptx::pack2(a[t], a[t]);
+      neg2[t] = ptx::pack2(ng, ng);
+    }
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld32<0>(t_s + 32, sb);
+    chunk_exp(sa, a2, neg2, acc0, acc1);
+    ptx::tmem_st16<0>(t_s, sa);
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld32<0>(t_s + 64, sa);
+    chunk_exp(sb, a2, neg2, acc0, acc1);
+    ptx::tmem_st16<0>(t_s + 16, sb);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float ng = fmaf(-kMagicF, a[4 + t], -m_ref);
+      a2[t] = ptx::pack2(a[4 + t], a[4 + t]);
+      neg2[t] = ptx::pack2(ng, ng);
+    }
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld32<0>(t_s + 96, sb);
+    chunk_exp(sa, a2, neg2, acc0, acc1);
+    ptx::tmem_st16<0>(t_s + 32, sa);
+    ptx::tmem_wait_ld();
+    chunk_exp(sb, a2, neg2, acc0, acc1);
+    ptx::tmem_st16<0>(t_s + 48, sb);
+    float sum0, sum1, sum2, sum3;
+    ptx::unpack2(acc0, sum0, sum1);
+    ptx::unpack2(acc1, sum2, sum3);
+    d_sum = d_sum * shrink + ((sum0 + sum1) + (sum2 + sum3));
+    return;
+  }
+
+  // ---- a block with masked columns (the diagonal of a causal launch, the ragged end of the keys): plain
+  // code, 64 columns at a time
   float m_blk = -INFINITY;
 #pragma unroll 1
   for (int hf = 0; hf < 2; ++hf) {
@@ -128,116 +277,40 @@ __device__ __forceinline__ void softmax_block(uint32_t t_s, const float (&a)[8],
     ptx::tmem_ld32<0>(t_s + hf * 64, s);
     ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
     ptx::tmem_wait_ld();
-    if (!need_mask) {
-      // per scale class: integer maximum (three-input), then one conversion and one multiply
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {                       // the class owns columns 2t + 8i, 2t + 8i + 1
-        int v[16];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[2 * i] = static_cast<int>(s[2 * t + 8 * i]);
-          v[2 * i + 1] = static_cast<int>(s[2 * t + 8 * i + 1]);
-        }
-        int mx = v[0];
-#pragma unroll
-        for (int i = 1; i < 15; i += 2) mx = __vimax3_s32(mx, v[i], v[i + 1]);
-        mx = max(mx, v[15]);
-        const float at = hf ? a[4 + t] : a[t];
-        m_blk = fmaxf(m_blk, static_cast<float>(mx) * at);
-      }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
-        const float x = static_cast<float>(static_cast<int>(s[c])) * at;
-        m_blk = fmaxf(m_blk, (hf * 64 + c <= lim) ? x : -INFINITY);
-      }
+    for (int c = 0; c < 64; ++c) {
+      const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
+      const float x = static_cast<float>(static_cast<int>(s[c])) * at;
+      m_blk = fmaxf(m_blk, (hf * 64 + c <= lim) ? x : -INFINITY);
     }
   }
-
-  // new reference: integer, at least this block's maximum, never below anything already used, and
-  // not below the other warpgroup's reference of block j-3.  That block's softmax finished before
-  // the scores of block j could be issued, so the value is always the same one: results do not depend
-  // on how the two warpgroups happen to interleave.
-  // (references move in steps of kRefStep: coarse enough that the two warpgroups nearly always agree
-  // and the fold stays a plain add, fine enough that P keeps its fp16 precision: P's largest value in
-  // a row is at least 2^-kRefStep)
-  const float r_new = fmaxf(fmaxf(ref, ceilf(m_blk * (1.0f / kRefStep)) * kRefStep), r_other);
-  // a row that has seen nothing visible yet keeps a finite reference so that 2^(-inf - m) = 0
+  const float r_new = next_reference(ref, m_blk, r_other);
   const float m_ref = (r_new == -INFINITY) ? 0.0f : r_new;
   const float shrink = (ref == r_new) ? 1.0f : pow2_int(fmaxf(ref - m_ref, -127.0f));
   ref = r_new;
   *ref_pub_slot = r_new;
-  *ref_ring_slot = r_new;         // (slot reuse: the block eight before was folded, and read by the other warpgroup, long ago)
-
-  // pass 2: P = 2^(S*a - ref), packed to fp16 pairs; the P of keys [64 hf, 64 hf + 64) overwrites
-  // score columns [32 hf, 32 hf + 32), which pass 2 has already consumed
-  float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
-  // Share of 2^x evaluated with a polynomial on the FMA pipe instead of ex2.approx.  Here 0 is best
-  // (N = 32768 causal, sustained: 18.1 ms with 0/8, 18.4 with 1/8, 18.9 with 2/8, 19.6 with 3/8): with
-  // two warpgroups out of phase the special-function unit is not the limiter and the extra
-  // instructions only cost power.  The two-tile kernel (attn_v1.cuh) is issue-bound and keeps 3/8.
-#ifndef SAGE_V4_POLY
-#define SAGE_V4_POLY 0
-#endif
-  constexpr int kPolyDen = 8, kPolyNum = SAGE_V4_POLY;
+  *ref_ring_slot = r_new;
+  float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll 1
   for (int hf = 0; hf < 2; ++hf) {
     uint32_t s[64];
     ptx::tmem_ld32<0>(t_s + hf * 64, s);
     ptx::tmem_ld32<32>(t_s + hf * 64 + 32, s);
     ptx::tmem_wait_ld();
-    if (!need_mask) {
-      // X = float(S) + 1.5*2^23 without a conversion (|S| < 2^22), then p = 2^(X*a + neg) with
-      // neg = -(1.5*2^23*a + ref); two columns of one class per packed FMA
-      unsigned long long a2[4], neg2[4];
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float at = hf ? a[4 + t] : a[t];
-        const float ng = fmaf(-kMagicF, at, -m_ref);
-        a2[t] = ptx::pack2(at, at);
-        neg2[t] = ptx::pack2(ng, ng);
-      }
-      unsigned long long acc0 = ptx::pack2(sum0, sum1), acc1 = ptx::pack2(sum2, sum3);
-#pragma unroll
-      for (int c = 0; c < 64; c += 4) {
-        const unsigned long long e0 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 0] + kMagicI), __uint_as_float(s[c + 1] + kMagicI)),
-                                                a2[(c & 7) >> 1], neg2[(c & 7) >> 1]);
-        const unsigned long long e1 = ptx::fma2(ptx::pack2(__uint_as_float(s[c + 2] + kMagicI), __uint_as_float(s[c + 3] + kMagicI)),
-                                                a2[((c + 2) & 7) >> 1], neg2[((c + 2) & 7) >> 1]);
-        float p0, p1, p2, p3;
-        if (((c >> 2) % kPolyDen) < kPolyNum) {
-          ptx::exp2_pair_poly(e0, p0, p1);
-          ptx::exp2_pair_poly(e1, p2, p3);
-        } else {
-          float x0, x1, x2, x3;
-          ptx::unpack2(e0, x0, x1);
-          ptx::unpack2(e1, x2, x3);
-          p0 = ptx::ex2(x0), p1 = ptx::ex2(x1), p2 = ptx::ex2(x2), p3 = ptx::ex2(x3);
-        }
-        acc0 = ptx::add2(acc0, ptx::pack2(p0, p1));
-        acc1 = ptx::add2(acc1, ptx::pack2(p2, p3));
-        s[c / 2 + 0] = ptx::pack_f16x2(p0, p1);
-        s[c / 2 + 1] = ptx::pack_f16x2(p2, p3);
-      }
-      ptx::unpack2(acc0, sum0, sum1);
-      ptx::unpack2(acc1, sum2, sum3);
-    } else {
-#pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
-        const float x0 = static_cast<float>(static_cast<int>(s[c + 0])) * at;
-        const float x1 = static_cast<float>(static_cast<int>(s[c + 1])) * at;
-        const float p0 = (hf * 64 + c <= lim) ? ptx::ex2(x0 - m_ref) : 0.0f;
-        const float p1 = (hf * 64 + c + 1 <= lim) ? ptx::ex2(x1 - m_ref) : 0.0f;
-        sum0 += p0;
-        sum1 += p1;
-        s[c / 2] = ptx::pack_f16x2(p0, p1);
-      }
+    for (int c = 0; c < 64; c += 2) {
+      const float at = hf ? a[4 + ((c & 7) >> 1)] : a[(c & 7) >> 1];
+      const float x0 = static_cast<float>(static_cast<int>(s[c + 0])) * at;
+      const float x1 = static_cast<float>(static_cast<int>(s[c + 1])) * at;
+      const float p0 = (hf * 64 + c <= lim) ? ptx::ex2(x0 - m_ref) : 0.0f;
+      const float p1 = (hf * 64 + c + 1 <= lim) ? ptx::ex2(x1 - m_ref) : 0.0f;
+      sum0 += p0;
+      sum1 += p1;
+      s[c / 2] = ptx::pack_f16x2(p0, p1);
     }
     ptx::tmem_st32<0>(t_s + hf * 32, s);
   }
-  d_sum = d_sum * shrink + ((sum0 + sum1) + (sum2 + sum3));
+  d_sum = d_sum * shrink + (sum0 + sum1);
 }
 
 // ---------------------------------------------------------------------------------------------------
