@@ -200,7 +200,7 @@ def cpu_baseline(w, seconds_hint=20.0):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel in the ncu capture named in
 # roofline.traffic_unit; re-measured whenever the kernel changes
-NCU_TRAFFIC_4K = 179.0e6
+NCU_TRAFFIC_4K = 179.6e6
 
 REF_CFG = (128, 64, 32, 64)          # the reference's first candidate and fallback (sageattention/cuda_autotune.py:9-14)
 REF_OPS = {"fp32": "qk_int8_sv_f16_accum_f32_attn", "fp16": "qk_int8_sv_f16_accum_f16_attn",
