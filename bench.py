@@ -494,7 +494,7 @@ def main():
 
     # ---- the same step with the output exchanged (every rank ends with all heads): rows stored into every
     # rank's buffer by the attention epilogue, or NCCL all-gathers overlapped per head group (sageattn_sharded)
-    gather_ms = plain_again_ms = None
+    gather_ms = plain_again_ms = gather_used = None
     if world > 1 and not args.no_gather:
         def step_gather():
             out_holder["g"] = sageattn_sharded(q, k, v, num_q_heads=w["Hq"], num_kv_heads=w["Hkv"], gather=True,
@@ -503,6 +503,8 @@ def main():
         # the plain step once more, right after: the two loops run minutes apart under a power cap, and the
         # difference between them is only meaningful next to the drift of the plain step itself
         plain_again_ms = timed(step, args.steps, 1) / args.steps
+        from sageattention.parallel import last_gather_via
+        gather_used = last_gather_via()            # "peer", or "nccl" when the peer buffers could not be had
 
     # ---- end to end from pinned host memory
     e2e = None
@@ -536,7 +538,7 @@ def main():
                                      "(sage_b200_launch_count) on rank 0, times the number of ranks",
                 "gather_ms_per_step": gather_ms, "ms_per_step_after_gather_loop": plain_again_ms,
                 "gather_overhead_ms": (gather_ms - 0.5 * (ms_per_step + plain_again_ms)) if gather_ms else None,
-                "gather_via": args.gather_via if gather_ms else None,
+                "gather_via": gather_used if gather_ms else None,
                 "value_with_gather": (F_lit / (gather_ms * 1e-3) / 1e12) if gather_ms else None}
         if not args.no_ref_gpu and world == 1 and reference_gpu_available(w):
             # the reference's own GPU kernels on the same inputs, after (never inside) the timed region

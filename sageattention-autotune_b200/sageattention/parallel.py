@@ -140,6 +140,13 @@ class PeerOutput:
 
 
 _peer_outputs = {}
+_last_exchange = {"via": None}
+
+
+def last_gather_via() -> Optional[str]:
+    """How the last gathering sageattn_sharded call of this process exchanged the output: "peer", "nccl"
+    (or the caller's backend), or None before the first such call."""
+    return _last_exchange["via"]
 
 
 def _peer_output(shape, dtype, device, group) -> Optional[PeerOutput]:
@@ -236,7 +243,10 @@ def sageattn_sharded(q_local, k_local, v_local, num_q_heads: int, tensor_layout:
         kv = num_q_heads if num_kv_heads is None else num_kv_heads
         res = _sharded_into_peers(q_local, k_local, v_local, num_q_heads, kv, tensor_layout, group, attn_fn, kwargs)
         if res is not None:
+            _last_exchange["via"] = "peer"
             return res
+    if gather and dist.is_initialized() and dist.get_world_size(group) > 1:
+        _last_exchange["via"] = dist.get_backend(group)
     if attn_fn is None:
         from .core import sageattn as attn_fn
     h_dim = 1 if tensor_layout == "HND" else 2
