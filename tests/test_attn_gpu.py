@@ -522,3 +522,26 @@ def test_host_buffer_entry_point_equals_the_device_call(layout, Hq, Hkv, chunk):
     assert torch.equal(got, exp.cpu())
     with pytest.raises(ValueError):
         sageattn_host(q.cuda(), k, v)
+
+
+def test_host_buffer_entry_point_replays_a_captured_step():
+    """With pinned buffers whose head groups are contiguous the second call with the same tensors replays a
+    CUDA graph of the whole pipelined step: same bits as the step-by-step call, and new contents of the
+    same buffers are picked up."""
+    import sageattention
+    from sageattention import host
+    cuda_or_fail()
+    q, k, v = make_qkv(1, 12, 6, 1000, 128, torch.float16, "HND", seed=78, k_bias=1.0, device="cpu")
+    q, k, v = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+    kw = dict(tensor_layout="HND", kv_heads_per_chunk=2, is_causal=True)
+    first = host.sageattn_host(q, k, v, out=out, **kw).clone()
+    plan = next(reversed(host._plans.values()))
+    assert plan.graph is not None, "the step was not captured"
+    second = host.sageattn_host(q, k, v, out=out, **kw).clone()
+    exp = sageattention.sageattn(q.cuda(), k.cuda(), v.cuda(), tensor_layout="HND", is_causal=True).cpu()
+    assert torch.equal(first, exp) and torch.equal(second, exp)
+    q.neg_()                                                   # same buffers, new contents
+    third = host.sageattn_host(q, k, v, out=out, **kw)
+    exp3 = sageattention.sageattn(q.cuda(), k.cuda(), v.cuda(), tensor_layout="HND", is_causal=True).cpu()
+    assert torch.equal(third, exp3) and not torch.equal(exp3, exp)
