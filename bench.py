@@ -60,6 +60,8 @@ def bind_host_to_gpu(index: int):
     """Pin this process to the CPUs NVML reports as local to GPU `index` before any pinned host buffer
     is allocated, so that the buffers of the end-to-end leg land on the GPU's NUMA node (first touch)
     whichever core the launcher happened to start the process on.  Returns a description or None."""
+    if os.environ.get("SAGE_B200_BENCH_BIND", "1") == "0":
+        return {"cpus": None, "source": "unchanged (SAGE_B200_BENCH_BIND=0)"}
     try:
         import pynvml
         pynvml.nvmlInit()
