@@ -24,8 +24,8 @@
 
 namespace sage {
 
-constexpr int kSeqBucketEdges[] = {1024, 2048, 4096, 16384, 65536};
-constexpr int kSeqBuckets = 6;
+constexpr int kSeqBucketEdges[] = {1024, 2048, 4096, 6144, 8192, 16384, 65536};
+constexpr int kSeqBuckets = 8;
 
 inline int seq_bucket(int len_kv) {
   for (int i = 0; i < kSeqBuckets - 1; ++i)
@@ -43,13 +43,16 @@ inline sage_b200_tile_entry tile_lookup(int head_dim, int is_causal, int pv_accu
     //   D 128 causal  H 64:  N 1024  0.048 / 0.063    N 4096  0.349 / 0.507    N 32768  16.2 / 24.3
     //   D  64 full    B 16 H 10 N 4096:  1.29 / 1.49
     // and its persistent form (one CTA per SM walking over the tiles) against one CTA per tile:
-    //   D 128 causal  H 64:  N 1024  0.042 / 0.048    N 4096  0.339 / 0.353    N 16384  4.68 / 4.04    N 32768  20.8 / 16.2
-    //   D  64 full    B 16 H 10 N 4096:  1.20 / 1.29
+    //   D 128 causal  H 64:  N 1024  0.047 / 0.051   N 4096  0.336 / 0.369   N 6144  0.661 / 0.694   N 8192  1.128 / 1.115
+    //                        N 16384  4.38 / 3.78    N 32768  18.9 / 15.8
+    //   D 128 full    H 32 N 8192:  0.991 / 0.945
+    //   D  64 full    B 16 H 10 N 4096:  1.098 / 1.159        B 4 H 10 N 8192:  1.054 / 1.099
     // The persistent form hides a tile's set-up and epilogue, which is what short sequences consist of;
-    // it deals tiles round-robin across all heads, so from N = 8192 on the CTAs running together no
-    // longer share K/V in L2 and the one-CTA-per-tile form (tiles of one head launched next to each
-    // other) wins.
-    e.kernel = (bucket <= 2) ? SAGE_B200_KERNEL_ONE_TILE_PERSISTENT : SAGE_B200_KERNEL_ONE_TILE_FOLD;
+    // it deals tiles round-robin across all heads, so once a head's K/V no longer stays in L2 next to
+    // the other heads' (N = 8192 at 128 channels, later at 64) the one-CTA-per-tile form (tiles of one
+    // head launched next to each other) wins.
+    const bool persistent = bucket <= 3 || (head_dim == 64 && bucket <= 4);
+    e.kernel = persistent ? SAGE_B200_KERNEL_ONE_TILE_PERSISTENT : SAGE_B200_KERNEL_ONE_TILE_FOLD;
     e.q_tiles_per_cta = 1;
   } else {
     e.kernel = (pv_accum == SAGE_B200_PV_F16_F32) ? SAGE_B200_KERNEL_TWO_TILE_COUPLED : SAGE_B200_KERNEL_TWO_TILE;

@@ -111,6 +111,22 @@ def test_sd_shape_matches_reference_kernel(mode):
     print("sd", mode, close_on_device(out, ref_out, ("sd", mode)))
 
 
+@pytest.mark.parametrize("B,H,N,D,causal,dtype", [(1, 16, 6000, 128, True, torch.float16),       # persistent one-tile kernel
+                                                  (1, 16, 6200, 128, True, torch.bfloat16),      # one CTA per tile
+                                                  (2, 10, 8100, 64, False, torch.float16)])      # persistent at 64 channels
+def test_lengths_around_the_tables_kernel_switch_match_reference_kernel(B, H, N, D, causal, dtype):
+    """Key lengths on both sides of the tile table's switch between the persistent one-tile kernel and one
+    CTA per tile (6144 keys at 128 channels, 8192 at 64), ragged on purpose."""
+    from sageattention.tile_table import select_entry
+    q, k, v = device_qkv(B, H, H, N, D, dtype, "HND", seed=11, k_bias=1.0)
+    q8, qs, k8, ks, v16, _ = quantise(q, k, v, "HND")
+    out, ref_out, lse = ours_and_reference((q8, qs, k8, ks, v16), q, "HND", causal, "fp16+fp32", return_lse=True)
+    kernel = select_entry(D, causal, "fp16+fp32", N)["kernel"]
+    print(N, D, kernel, close_on_device(out, ref_out, (N, D, kernel)))
+    exp = dequantised_scores_lse(q8, qs, k8, ks, B - 1, H - 1, H - 1, "HND", causal, D ** -0.5)
+    assert float((lse[B - 1, H - 1] - exp).abs().max()) <= 2e-2
+
+
 def test_gqa_prefill_shape_matches_reference_kernel_and_lse():
     q, k, v = device_qkv(4, 32, 8, 8192, 128, torch.bfloat16, "NHD", seed=2, k_outliers=20.0)
     q8, qs, k8, ks, v16, _ = quantise(q, k, v, "NHD")
