@@ -115,7 +115,8 @@ class PeerOutput:
             dist.all_gather_object(flags, self.ok, group=group)
             self.ok = all(flags)
             if not self.ok:
-                self.reason = L.sage_b200_last_error().decode()
+                self.reason = L.sage_b200_last_error().decode() or "a peer could not allocate or map its buffer"
+                self.close()                                          # nothing half-built stays behind
                 break
             raw = torch.as_tensor(_RawCuda(ptr.value, self.nbytes), device=device)
             n = int(torch.Size(shape).numel())
