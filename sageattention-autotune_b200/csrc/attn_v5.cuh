@@ -80,8 +80,9 @@ struct SmemPlan {
   static constexpr int kDynamic = kTotal + 1024;             // slack for manual 1024-byte alignment
 };
 
-// The tiles of this CTA, in order.  Item i of the launch is tile (i / planes) of plane (i % planes), counted
-// from the last tile down when causal (heaviest first); CTA c takes items c, c + gridDim.x, ...
+// The tiles of this CTA, in order; CTA c takes items c, c + gridDim.x, ...  In a causal launch item i is tile
+// (i / planes) of plane (i % planes), counted from the last tile down (heaviest first); otherwise it is tile
+// (i % tiles) of plane (i / tiles).
 struct TileWalk {
   int item, tiles, planes, total;
   int tile, h, b, q0, n_blk;
@@ -95,7 +96,12 @@ struct TileWalk {
   __device__ __forceinline__ bool valid() const { return item < total; }
   __device__ __forceinline__ void load(const AttnParams& p) {
     if (item >= total) return;
-    const int rank = item / planes, plane = item - rank * planes;
+    int rank, plane;
+    if (p.causal) {            // all planes' heaviest tiles first: balances the CTAs without atomics
+      rank = item / planes, plane = item - rank * planes;
+    } else {                   // equal tiles: plane after plane, so that the CTAs running together share K/V in L2
+      plane = item / tiles, rank = item - plane * tiles;
+    }
     tile = p.causal ? (tiles - 1 - rank) : rank;
     h = plane % p.heads_q;
     b = plane / p.heads_q;

@@ -45,13 +45,17 @@ inline sage_b200_tile_entry tile_lookup(int head_dim, int is_causal, int pv_accu
     // and its persistent form (one CTA per SM walking over the tiles) against one CTA per tile:
     //   D 128 causal  H 64:  N 1024  0.047 / 0.051   N 4096  0.336 / 0.369   N 6144  0.661 / 0.694   N 8192  1.128 / 1.115
     //                        N 16384  4.38 / 3.78    N 32768  18.9 / 15.8
-    //   D 128 full    H 32 N 8192:  0.991 / 0.945
-    //   D  64 full    B 16 H 10 N 4096:  1.098 / 1.159        B 4 H 10 N 8192:  1.054 / 1.099
+    //   D  64 causal: as D 128 up to 8192 keys
     // The persistent form hides a tile's set-up and epilogue, which is what short sequences consist of;
     // it deals tiles round-robin across all heads, so once a head's K/V no longer stays in L2 next to
     // the other heads' (N = 8192 at 128 channels, later at 64) the one-CTA-per-tile form (tiles of one
     // head launched next to each other) wins.
-    const bool persistent = bucket <= 3 || (head_dim == 64 && bucket <= 4);
+    // Without a causal mask all tiles weigh the same and the persistent form walks plane after plane, so the
+    // CTAs running together do share K/V; it then stays ahead a little longer:
+    //   D 128 full  H 32 N 8192  0.934 / 0.946   H 16 N 16384  1.792 / 1.772   H 8 N 32768  3.47 / 3.40
+    //   D  64 full  B 16 H 10 N 4096  1.054 / 1.159   B 4 H 10 N 8192  1.064 / 1.099   B 2 H 10 N 16384  2.087 / 2.109
+    const bool persistent = is_causal ? (bucket <= 3 || (head_dim == 64 && bucket <= 4))
+                                      : (bucket <= 4 || (head_dim == 64 && bucket <= 5));
     e.kernel = persistent ? SAGE_B200_KERNEL_ONE_TILE_PERSISTENT : SAGE_B200_KERNEL_ONE_TILE_FOLD;
     e.q_tiles_per_cta = 1;
   } else {
@@ -63,7 +67,6 @@ inline sage_b200_tile_entry tile_lookup(int head_dim, int is_causal, int pv_accu
     //   D 128 H 8 N 4096 (a launch of 128 CTAs):  causal 0.069 / 0.084   full 0.071 / 0.110
     e.q_tiles_per_cta = (head_dim == 256) ? 1 : 2;
   }
-  (void)is_causal;
   return e;
 }
 

@@ -113,10 +113,12 @@ def test_sd_shape_matches_reference_kernel(mode):
 
 @pytest.mark.parametrize("B,H,N,D,causal,dtype", [(1, 16, 6000, 128, True, torch.float16),       # persistent one-tile kernel
                                                   (1, 16, 6200, 128, True, torch.bfloat16),      # one CTA per tile
-                                                  (2, 10, 8100, 64, False, torch.float16)])      # persistent at 64 channels
+                                                  (2, 10, 8100, 64, False, torch.float16),       # persistent at 64 channels
+                                                  (1, 8, 8300, 128, False, torch.float16),       # one CTA per tile, no mask
+                                                  (1, 10, 16500, 64, False, torch.bfloat16)])
 def test_lengths_around_the_tables_kernel_switch_match_reference_kernel(B, H, N, D, causal, dtype):
     """Key lengths on both sides of the tile table's switch between the persistent one-tile kernel and one
-    CTA per tile (6144 keys at 128 channels, 8192 at 64), ragged on purpose."""
+    CTA per tile (causal: 6144 keys at 128 channels, 8192 at 64; otherwise 8192 and 16384), ragged on purpose."""
     from sageattention.tile_table import select_entry
     q, k, v = device_qkv(B, H, H, N, D, dtype, "HND", seed=11, k_bias=1.0)
     q8, qs, k8, ks, v16, _ = quantise(q, k, v, "HND")

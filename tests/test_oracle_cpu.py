@@ -209,8 +209,12 @@ def test_tile_table_is_total_and_consistent():
     assert select_entry(128, True, "fp16+fp32", 8192)["kernel"] == "one_tile_fold"
     assert select_entry(128, True, "fp16+fp32", 6144)["kernel"] == "one_tile_persistent"
     assert select_entry(128, True, "fp16+fp32", 6145)["kernel"] == "one_tile_fold"
-    assert select_entry(64, False, "fp16+fp32", 8192)["kernel"] == "one_tile_persistent"
-    assert select_entry(64, False, "fp16+fp32", 8193)["kernel"] == "one_tile_fold"
+    assert select_entry(64, True, "fp16+fp32", 8192)["kernel"] == "one_tile_persistent"
+    assert select_entry(64, True, "fp16+fp32", 8193)["kernel"] == "one_tile_fold"
+    assert select_entry(128, False, "fp16+fp32", 8192)["kernel"] == "one_tile_persistent"
+    assert select_entry(128, False, "fp16+fp32", 8193)["kernel"] == "one_tile_fold"
+    assert select_entry(64, False, "fp16+fp32", 16384)["kernel"] == "one_tile_persistent"
+    assert select_entry(64, False, "fp16+fp32", 16385)["kernel"] == "one_tile_fold"
     # ... in its persistent form (one CTA per SM walking over the tiles) up to 4096 keys
     assert select_entry(64, False, "fp16+fp32", 4096)["kernel"] == "one_tile_persistent"
     assert select_entry(128, True, "fp16+fp32", 1024)["kernel"] == "one_tile_persistent"
